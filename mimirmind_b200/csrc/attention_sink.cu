@@ -186,7 +186,8 @@ __global__ void attention_sink_generic_kernel(const T* __restrict__ q, const T* 
                                               const int32_t* __restrict__ positions, const int32_t* __restrict__ token_req,
                                               const int32_t* __restrict__ block_table, int table_width, int page_size,
                                               int n_tokens, int H, int G, int dk, int dv, int window, float scale, int sink,
-                                              const float* __restrict__ sink_logit, const float* __restrict__ dist_bias, int dist_max) {
+                                              const float* __restrict__ sink_logit, const float* __restrict__ dist_bias, int dist_max,
+                                              float softcap, int Gv, int v_row) {
     extern __shared__ float q_smem[];  // [warps][dk]
     const int warps_per_block = blockDim.x >> 5;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -211,7 +212,9 @@ __global__ void attention_sink_generic_kernel(const T* __restrict__ q, const T* 
 #pragma unroll
     for (int a = 0; a < SINK_MAX_ACC; ++a) acc[a] = 0.0f;
     const size_t k_head = (size_t)g * page_size * dk, k_stride = (size_t)G * page_size * dk;
-    const size_t v_head = (size_t)g * page_size * dv, v_stride = (size_t)G * page_size * dv;
+    // values: Gv heads of which key head g reads g mod Gv, consecutive tokens v_row numbers apart (a pool of its own: dv)
+    const size_t v_head = (size_t)(g % Gv) * page_size * v_row, v_stride = (size_t)Gv * page_size * v_row;
+    const float inv_cap = softcap > 0.0f ? 1.0f / softcap : 0.0f;
 
     for (int c = (lo / 32) * 32; c < hi; c += 32) {
         const int j = c + lane;
@@ -222,6 +225,7 @@ __global__ void attention_sink_generic_kernel(const T* __restrict__ q, const T* 
             const T* kr = k_pages + (size_t)page * k_stride + k_head + (size_t)(j % page_size) * dk;
             float dot = 0.0f;
             for (int d = 0; d < dk; ++d) dot = fmaf(qs[d], to_f32<T>(kr[d]), dot);
+            if (softcap > 0.0f) dot = softcap * tanhf(dot * inv_cap);      // the scaled score, bent into (-cap, cap)
             // a learned bias per (distance, head), not scaled: the table's last row stands for every larger distance
             s = dist_bias ? dot + dist_bias[(size_t)h * (dist_max + 1) + min(pos - j, dist_max)] : dot;
         }
@@ -236,7 +240,7 @@ __global__ void attention_sink_generic_kernel(const T* __restrict__ q, const T* 
             if (key < lo || key >= hi) continue;  // uniform over the warp
             const float pj = __shfl_sync(0xffffffffu, p, jj);
             const int page = table[key / page_size];
-            const T* vr = v_pages + (size_t)page * v_stride + v_head + (size_t)(key % page_size) * dv;
+            const T* vr = v_pages + (size_t)page * v_stride + v_head + (size_t)(key % page_size) * v_row;
 #pragma unroll
             for (int a = 0; a < SINK_MAX_ACC; ++a) {
                 const int d = a * 32 + lane;
@@ -257,8 +261,10 @@ __global__ void attention_sink_generic_kernel(const T* __restrict__ q, const T* 
 MM_EXPORT int mm_attention_sink_generic(const void* q, const void* k_pages, const void* v_pages, void* out, int dtype,
                                         const void* positions, const void* token_req, const void* block_table,
                                         int table_width, int page_size, int n_tokens, int H, int G, int dk, int dv, int window,
-                                        float scale, int sink, const void* sink_logit, const void* dist_bias, int dist_max, void* stream) {
+                                        float scale, int sink, const void* sink_logit, const void* dist_bias, int dist_max, float softcap,
+                                        int Gv, int v_row, void* stream) {
     MM_REQUIRE(dist_bias == nullptr || dist_max >= 0, "attention: the distance table needs at least one row");
+    MM_REQUIRE(Gv >= 1 && G % Gv == 0 && v_row >= dv && softcap >= 0.0f, "attention: value heads must divide the key heads, a value row holds at least dv numbers");
     MM_REQUIRE(n_tokens >= 0 && H > 0 && G > 0 && dk > 0 && dv > 0 && H % G == 0, "attention: heads must be a positive multiple of kv heads");
     MM_REQUIRE(dv <= 32 * SINK_MAX_ACC && dk <= 2048, "attention: value size above 512 or key size above 2048 is not supported");
     MM_REQUIRE(page_size > 0 && table_width > 0 && window >= 0, "attention: bad page geometry or window");
@@ -272,12 +278,12 @@ MM_EXPORT int mm_attention_sink_generic(const void* q, const void* k_pages, cons
         mm_launch(attention_sink_generic_kernel<float>, dim3(blocks), dim3(warps * 32), smem, s, (const float*)q, (const float*)k_pages,
                   (const float*)v_pages, (float*)out, (const int32_t*)positions, (const int32_t*)token_req,
                   (const int32_t*)block_table, table_width, page_size, n_tokens, H, G, dk, dv, window, scale, sink,
-                  (const float*)sink_logit, (const float*)dist_bias, dist_max);
+                  (const float*)sink_logit, (const float*)dist_bias, dist_max, softcap, Gv, v_row);
     else if (dtype == MM_BF16)
         mm_launch(attention_sink_generic_kernel<__nv_bfloat16>, dim3(blocks), dim3(warps * 32), smem, s, (const __nv_bfloat16*)q,
                   (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, (__nv_bfloat16*)out, (const int32_t*)positions,
                   (const int32_t*)token_req, (const int32_t*)block_table, table_width, page_size, n_tokens, H, G, dk, dv, window,
-                  scale, sink, (const float*)sink_logit, (const float*)dist_bias, dist_max);
+                  scale, sink, (const float*)sink_logit, (const float*)dist_bias, dist_max, softcap, Gv, v_row);
     else
         MM_REQUIRE(false, "attention: dtype must be float32 or bfloat16");
     MM_CHECK_LAUNCH();

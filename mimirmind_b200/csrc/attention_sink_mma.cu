@@ -27,8 +27,9 @@
 template <int DK, int DV>
 __device__ __forceinline__ void load_kv_tile2(__nv_bfloat16* dK, __nv_bfloat16* dV, const __nv_bfloat16* __restrict__ kpool,
                                               const __nv_bfloat16* __restrict__ vpool, const int32_t* __restrict__ table,
-                                              int key0, int lo, int hi, int G, int g, int page_size, int page_shift) {
+                                              int key0, int lo, int hi, int G, int g, int page_size, int page_shift, int Gv) {
     constexpr int KS = DK + 8, VS = DV + 8, KC = DK / 8, VC = DV / 8;
+    const int gv = g % Gv;      // the value pool has Gv heads; key head g reads value head g mod Gv
     for (int c = threadIdx.x; c < SKT * KC; c += SATT_THREADS) {
         const int r = c / KC, part = c - r * KC;
         const int key = key0 + r;
@@ -48,7 +49,7 @@ __device__ __forceinline__ void load_kv_tile2(__nv_bfloat16* dK, __nv_bfloat16* 
         if (key >= lo && key < hi) {
             const int pidx = page_shift >= 0 ? (key >> page_shift) : (key / page_size);
             const int slot = key - pidx * page_size;
-            cp_async16(d, vpool + (((size_t)table[pidx] * G + g) * page_size + slot) * DV + part * 8);
+            cp_async16(d, vpool + (((size_t)table[pidx] * Gv + gv) * page_size + slot) * DV + part * 8);
         } else {
             *reinterpret_cast<uint4*>(d) = make_uint4(0, 0, 0, 0);
         }
@@ -66,7 +67,7 @@ __global__ void __launch_bounds__(SATT_THREADS) attention_sink_prefill_kernel(
     const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_pages,
     const __nv_bfloat16* __restrict__ v_pages, __nv_bfloat16* __restrict__ out, const int32_t* __restrict__ tiles,
     const int32_t* __restrict__ block_table, int table_width, int page_size, int H, int G, int window, float scale_log2,
-    int sink, const float* __restrict__ sink_logit, const float* __restrict__ dist_bias, int dist_max) {
+    int sink, const float* __restrict__ sink_logit, const float* __restrict__ dist_bias, int dist_max, float softcap, int Gv) {
     constexpr int KS = DK + 8, VS = DV + 8;
     constexpr int KSTEPS = DK / 16;
     constexpr int NT_O = DV / 8;
@@ -93,7 +94,7 @@ __global__ void __launch_bounds__(SATT_THREADS) attention_sink_prefill_kernel(
         *reinterpret_cast<uint4*>(sQ + r * KS + part * 8) = v;
     }
     const int page_shift = (page_size & (page_size - 1)) == 0 ? __ffs(page_size) - 1 : -1;
-    load_kv_tile2<DK, DV>(sK, sV, k_pages, v_pages, table, kt_begin * SKT, lo_all, hi_all, G, g, page_size, page_shift);
+    load_kv_tile2<DK, DV>(sK, sV, k_pages, v_pages, table, kt_begin * SKT, lo_all, hi_all, G, g, page_size, page_shift, Gv);
     cp_async_commit();
     __syncthreads();
 
@@ -117,8 +118,10 @@ __global__ void __launch_bounds__(SATT_THREADS) attention_sink_prefill_kernel(
     // the sink: maximum 0 (raw score), mass 1 held by the first thread of the quad that shares a row.  With a learned
     // sink or a distance bias the scores are brought to their final form (scaled, bias added, in units of log2 e) right
     // after the product, and from there on the scale is 1; the learned sink then starts the maximum at its logit.
-    const bool ext = sink_logit != nullptr || dist_bias != nullptr;
+    // A soft cap bends the scaled score into (-cap, cap): s <- cap tanh(s / cap), before any bias.
+    const bool ext = sink_logit != nullptr || dist_bias != nullptr || softcap > 0.0f;
     const float sl2 = ext ? 1.0f : scale_log2;
+    const float cap_in = softcap > 0.0f ? scale_log2 / (SINK_LOG2E_F * softcap) : 0.0f, cap_out = softcap * SINK_LOG2E_F;
     const float* bias_h = dist_bias ? dist_bias + (size_t)h * (dist_max + 1) : nullptr;
     const float l0 = ((sink || sink_logit) && (lane & 3) == 0) ? 1.0f : 0.0f;
     float m_lo = sink_logit ? sink_logit[h] * SINK_LOG2E_F : (sink ? 0.0f : -INFINITY), m_hi = m_lo, l_lo = l0, l_hi = l0;
@@ -127,7 +130,7 @@ __global__ void __launch_bounds__(SATT_THREADS) attention_sink_prefill_kernel(
         const int buf = (kt - kt_begin) & 1;
         if (kt + 1 < kt_end) {
             load_kv_tile2<DK, DV>(sK + (buf ^ 1) * SKT * KS, sV + (buf ^ 1) * SKT * VS, k_pages, v_pages, table, (kt + 1) * SKT,
-                                  lo_all, hi_all, G, g, page_size, page_shift);
+                                  lo_all, hi_all, G, g, page_size, page_shift, Gv);
             cp_async_commit();
             cp_async_wait<1>();
         } else {
@@ -173,7 +176,7 @@ __global__ void __launch_bounds__(SATT_THREADS) attention_sink_prefill_kernel(
                             const int dist = (e >= 2 ? pos_hi : pos_lo) - key;
                             b = bias_h[min(max(dist, 0), dist_max)] * SINK_LOG2E_F;
                         }
-                        s[j][e] = fmaf(s[j][e], scale_log2, b);
+                        s[j][e] = softcap > 0.0f ? fmaf(tanhf(s[j][e] * cap_in), cap_out, b) : fmaf(s[j][e], scale_log2, b);
                     }
                 }
             }
@@ -260,12 +263,13 @@ __global__ void __launch_bounds__(SATT_THREADS) attention_sink_decode_kernel(
     float* __restrict__ part_ml, const int32_t* __restrict__ items,
     const int32_t* __restrict__ positions, const int32_t* __restrict__ token_req, const int32_t* __restrict__ block_table,
     int table_width, int page_size, int H, int G, int window, float scale_log2, int sink, const float* __restrict__ sink_logit,
-    const float* __restrict__ dist_bias, int dist_max) {
+    const float* __restrict__ dist_bias, int dist_max, float softcap, int Gv) {
     constexpr int KS = DK + 8, VS = DV + 8;
     constexpr int KSTEPS = DK / 16;
     constexpr int NT_O = DV / 8;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __nv_bfloat16* sK = reinterpret_cast<__nv_bfloat16*>(smem_raw);  // [STAGES][64][KS]
+    const float cap_in = softcap > 0.0f ? scale_log2 / (SINK_LOG2E_F * softcap) : 0.0f, cap_out = softcap * SINK_LOG2E_F;
     __nv_bfloat16* sV = sK + SDEC_STAGES * SKT * KS;                 // [STAGES][64][VS]
 
     const int item = blockIdx.x, g = blockIdx.y;
@@ -287,7 +291,7 @@ __global__ void __launch_bounds__(SATT_THREADS) attention_sink_decode_kernel(
     for (int st = 0; st < SDEC_STAGES - 1; ++st) {
         if (kt_begin + st < kt_end)
             load_kv_tile2<DK, DV>(sK + st * SKT * KS, sV + st * SKT * VS, k_pages, v_pages, table, (kt_begin + st) * SKT, k_begin, k_end,
-                                  G, g, page_size, page_shift);
+                                  G, g, page_size, page_shift, Gv);
         cp_async_commit();
     }
     uint32_t qf[KSTEPS][4];
@@ -316,7 +320,7 @@ __global__ void __launch_bounds__(SATT_THREADS) attention_sink_decode_kernel(
             if (nxt < kt_end) {
                 const int nb = (nxt - kt_begin) % SDEC_STAGES;
                 load_kv_tile2<DK, DV>(sK + nb * SKT * KS, sV + nb * SKT * VS, k_pages, v_pages, table, nxt * SKT, k_begin, k_end, G, g,
-                                      page_size, page_shift);
+                                      page_size, page_shift, Gv);
             }
             cp_async_commit();
             cp_async_wait<SDEC_STAGES - 1>();
@@ -345,7 +349,7 @@ __global__ void __launch_bounds__(SATT_THREADS) attention_sink_decode_kernel(
                     const int key = key0 + j * 8 + (lane & 3) * 2 + (e & 1);
                     float v = -INFINITY;
                     if (key >= k_begin && key < k_end) {
-                        v = s[j][e] * scale_log2;
+                        v = softcap > 0.0f ? tanhf(s[j][e] * cap_in) * cap_out : s[j][e] * scale_log2;
                         // rows of the tile are the query heads of this kv head: the bias of (distance, head)
                         const int hq = g * qpg + (lane >> 2) + (e >= 2 ? 8 : 0);
                         if (dist_bias != nullptr && hq < H) v += dist_bias[(size_t)hq * (dist_max + 1) + min(pos - key, dist_max)] * SINK_LOG2E_F;
@@ -474,7 +478,7 @@ static const float SINK_LOG2E = 1.4426950408889634f;
 template <int DK, int DV>
 static int launch_sink_prefill(const void* q, const void* k, const void* v, void* out, const void* tiles, int n_tiles,
                                const void* table, int table_width, int page_size, int H, int G, int window, float scale, int sink,
-                               const void* sink_logit, const void* dist_bias, int dist_max,
+                               const void* sink_logit, const void* dist_bias, int dist_max, float softcap, int Gv,
                                cudaStream_t s) {
     const size_t smem = (size_t)(3 * 64 * (DK + 8) + 2 * 64 * (DV + 8)) * sizeof(__nv_bfloat16);
     auto kernel = attention_sink_prefill_kernel<DK, DV>;
@@ -485,7 +489,7 @@ static int launch_sink_prefill(const void* q, const void* k, const void* v, void
     }
     mm_launch(kernel, dim3(H, n_tiles), dim3(SATT_THREADS), smem, s, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k,
               (const __nv_bfloat16*)v, (__nv_bfloat16*)out, (const int32_t*)tiles, (const int32_t*)table, table_width, page_size, H, G,
-              window, scale * SINK_LOG2E, sink, (const float*)sink_logit, (const float*)dist_bias, dist_max);
+              window, scale * SINK_LOG2E, sink, (const float*)sink_logit, (const float*)dist_bias, dist_max, softcap, Gv);
     MM_CHECK_LAUNCH();
     return MM_OK;
 }
@@ -495,7 +499,7 @@ static int launch_sink_decode(const void* q, const void* k, const void* v, void*
                               const void* items, int n_items,
                               const void* positions, const void* token_req, const void* table, int table_width, int page_size,
                               int H, int G, int window, float scale, int sink, const void* sink_logit, const void* dist_bias, int dist_max,
-                              cudaStream_t s) {
+                              float softcap, int Gv, cudaStream_t s) {
     const size_t kv = (size_t)SDEC_STAGES * 64 * (DK + 8 + DV + 8) * sizeof(__nv_bfloat16);
     const size_t merge = (size_t)(4 * 16 * DV + 4 * 16 * 2) * sizeof(float);
     const size_t smem = kv > merge ? kv : merge;
@@ -508,7 +512,7 @@ static int launch_sink_decode(const void* q, const void* k, const void* v, void*
     mm_launch(kernel, dim3(n_items, G, n_splits), dim3(SATT_THREADS), smem, s, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k,
               (const __nv_bfloat16*)v, (__nv_bfloat16*)out, (float*)part_o, (float*)part_ml, (const int32_t*)items,
               (const int32_t*)positions, (const int32_t*)token_req, (const int32_t*)table, table_width, page_size, H, G, window,
-              scale * SINK_LOG2E, sink, (const float*)sink_logit, (const float*)dist_bias, dist_max);
+              scale * SINK_LOG2E, sink, (const float*)sink_logit, (const float*)dist_bias, dist_max, softcap, Gv);
     MM_CHECK_LAUNCH();
     if (n_splits > 1) {
         mm_launch(attention_sink_merge_kernel, dim3(n_items, H), dim3(DV >= 64 ? 64 : 32), 0, s, (__nv_bfloat16*)out, (const float*)part_o,
@@ -547,13 +551,14 @@ MM_EXPORT int mm_attention_sink_supported(int dk, int dv) {
 MM_EXPORT int mm_attention_sink_prefill_bf16(const void* q, const void* k_pages, const void* v_pages, void* out, const void* tiles,
                                              int n_tiles, const void* block_table, int table_width, int page_size, int H, int G,
                                              int dk, int dv, int window, float scale, int sink, const void* sink_logit, const void* dist_bias,
-                                             int dist_max, void* stream) {
+                                             int dist_max, float softcap, int Gv, void* stream) {
+    MM_REQUIRE(Gv >= 1 && G % Gv == 0 && softcap >= 0.0f, "sink attention: the value heads must divide the key heads");
     MM_REQUIRE(n_tiles >= 0 && H > 0 && G > 0 && H % G == 0, "sink attention: heads must be a positive multiple of kv heads");
     MM_REQUIRE(page_size > 0 && table_width > 0 && window >= 0 && scale > 0.0f, "sink attention: bad page geometry, window or scale");
     if (n_tiles == 0) return MM_OK;
     cudaStream_t s = (cudaStream_t)stream;
     SINK_DISPATCH(launch_sink_prefill, q, k_pages, v_pages, out, tiles, n_tiles, block_table, table_width, page_size, H, G, window, scale,
-                  sink, sink_logit, dist_bias, dist_max, s);
+                  sink, sink_logit, dist_bias, dist_max, softcap, Gv, s);
     mm_set_last_error("sink attention: key and value sizes must each be one of 32, 64, 96, 128");
     return MM_ERR_UNSUPPORTED;
 }
@@ -564,7 +569,9 @@ MM_EXPORT int mm_attention_sink_decode_bf16(const void* q, const void* k_pages, 
                                             void* part_ml, int n_splits, const void* items,
                                             int n_items, const void* positions, const void* token_req, const void* block_table,
                                             int table_width, int page_size, int H, int G, int dk, int dv, int window, float scale,
-                                            int sink, const void* sink_logit, const void* dist_bias, int dist_max, void* stream) {
+                                            int sink, const void* sink_logit, const void* dist_bias, int dist_max, float softcap, int Gv,
+                                            void* stream) {
+    MM_REQUIRE(Gv >= 1 && G % Gv == 0 && softcap >= 0.0f, "sink attention: the value heads must divide the key heads");
     MM_REQUIRE(n_splits >= 1 && n_splits <= 64 && (n_splits == 1 || (part_o != nullptr && part_ml != nullptr)),
                "sink attention: 1..64 splits, with scratch for more than one");
     MM_REQUIRE(n_items >= 0 && H > 0 && G > 0 && H % G == 0 && H / G <= 16, "sink attention: at most 16 query heads per kv head");
@@ -572,7 +579,7 @@ MM_EXPORT int mm_attention_sink_decode_bf16(const void* q, const void* k_pages, 
     if (n_items == 0) return MM_OK;
     cudaStream_t s = (cudaStream_t)stream;
     SINK_DISPATCH(launch_sink_decode, q, k_pages, v_pages, out, part_o, part_ml, n_splits, items, n_items, positions, token_req, block_table,
-                  table_width, page_size, H, G, window, scale, sink, sink_logit, dist_bias, dist_max, s);
+                  table_width, page_size, H, G, window, scale, sink, sink_logit, dist_bias, dist_max, softcap, Gv, s);
     mm_set_last_error("sink attention: key and value sizes must each be one of 32, 64, 96, 128");
     return MM_ERR_UNSUPPORTED;
 }

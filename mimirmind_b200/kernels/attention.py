@@ -38,8 +38,8 @@ def _sink_lib():
     if not _sink_declared:
         P, I, F = c_void_p, c_int, c_float
         _lib.declare("mm_attention_sink_supported", [I, I])
-        _lib.declare("mm_attention_sink_prefill_bf16", [P, P, P, P, P, I, P, I, I, I, I, I, I, I, F, I, P, P, I, P])
-        _lib.declare("mm_attention_sink_decode_bf16", [P, P, P, P, P, P, I, P, I, P, P, P, I, I, I, I, I, I, I, F, I, P, P, I, P])
+        _lib.declare("mm_attention_sink_prefill_bf16", [P, P, P, P, P, I, P, I, I, I, I, I, I, I, F, I, P, P, I, F, I, P])
+        _lib.declare("mm_attention_sink_decode_bf16", [P, P, P, P, P, P, I, P, I, P, P, P, I, I, I, I, I, I, I, F, I, P, P, I, F, I, P])
         _lib.declare("mm_attention_decode_tma_bf16_sink", [P, P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, I, I, P, P])
         _lib.declare("mm_attention_prefill_tcgen05_sink", [P, P, P, P, P, I, P, I, I, I, I, I, I, I, I, F, I, P, P])
         _sink_declared = True
@@ -93,20 +93,30 @@ def sink_plan(ctx, n_tokens: int, tile_rows: int = SINK_TILE_ROWS):
 
 
 def paged_sink_attention(q, cache, out, ctx, num_heads: int, num_kv_heads: int, key_dim: int, value_dim: int, window: int,
-                         scale: float, sink: bool, sink_logit=None, dist_bias=None) -> torch.Tensor:
+                         scale: float, sink: bool, sink_logit=None, dist_bias=None, softcap: float = 0.0, value_heads=None,
+                         k_pages=None, v_pages=None, value_row=None) -> torch.Tensor:
     """Windowed attention with a softmax sink over pools of keys ``[pages, G, page, key_dim]`` and values
     ``[pages, G, page, value_dim]``.  bfloat16 with key and value sizes the tensor-core kernels are built for: a tiled
     kernel for portions, a kernel that shares keys between the query heads of a KV head for single tokens; anything
-    else: the fp32-arithmetic kernel."""
-    k_pages, v_pages, table = cache.arrays["k"], cache.arrays["v"], cache.block_table
-    if (USE_SINK_MMA and q.dtype == torch.bfloat16 and scale > 0 and num_heads // num_kv_heads <= 16
+    else: the fp32-arithmetic kernel.
+
+    ``softcap`` > 0 bends the scaled score into ``cap * tanh(score / cap)``.  ``value_heads`` (a divisor of the key heads):
+    the value pool has that many heads and key head ``g`` reads value head ``g mod value_heads`` (several key heads over one
+    set of values).  ``k_pages`` / ``v_pages``: the pools, if they are not the cache's arrays ``k`` and ``v``; ``value_row``:
+    how many numbers lie between the values of consecutive tokens (values that are a slice of a wider per-token array)."""
+    table = cache.block_table
+    k_pages = cache.arrays["k"] if k_pages is None else k_pages
+    v_pages = cache.arrays["v"] if v_pages is None else v_pages
+    value_heads = num_kv_heads if value_heads is None else int(value_heads)
+    value_row = value_dim if value_row is None else int(value_row)
+    if (USE_SINK_MMA and value_row == value_dim and q.dtype == torch.bfloat16 and scale > 0 and num_heads // num_kv_heads <= 16
             and _sink_lib().mm_attention_sink_supported(key_dim, value_dim)):
         from .lib import check
         lib = _sink_lib()
         # equal key and value sizes of 64 or 128: the tcgen05 prefill kernel of the plain attention, told of the sink
         from . import attention_bf16
         # a learned sink or a distance bias: the mma.sync kernels take them, the tcgen05 and TMA kernels do not
-        extended = sink_logit is not None or dist_bias is not None
+        extended = sink_logit is not None or dist_bias is not None or softcap > 0 or value_heads != num_kv_heads
         sink_ptr = sink_logit.data_ptr() if sink_logit is not None else None
         bias_ptr = dist_bias.data_ptr() if dist_bias is not None else None
         dist_max = dist_bias.shape[1] - 1 if dist_bias is not None else 0
@@ -124,7 +134,7 @@ def paged_sink_attention(q, cache, out, ctx, num_heads: int, num_kv_heads: int, 
             check(lib.mm_attention_sink_prefill_bf16(q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), out.data_ptr(), tiles.data_ptr(),
                                                      n_tiles, table.data_ptr(), table.shape[1], cache.page_size, num_heads, num_kv_heads,
                                                      key_dim, value_dim, int(window), float(scale), int(bool(sink)), sink_ptr, bias_ptr, dist_max,
-                                                     stream),
+                                                     float(softcap), value_heads, stream),
                   "attention_sink_prefill_bf16")
         tma = None
         if n_items and USE_SINK_TMA_DECODE and not extended and key_dim == value_dim and key_dim in (64, 128) and cache.page_size in (8, 16, 32, 64):
@@ -156,8 +166,9 @@ def paged_sink_attention(q, cache, out, ctx, num_heads: int, num_kv_heads: int, 
                                                     items.data_ptr() if items is not None else None, n_items, ctx.positions.data_ptr(),
                                                     ctx.token_req.data_ptr(), table.data_ptr(), table.shape[1], cache.page_size, num_heads,
                                                     num_kv_heads, key_dim, value_dim, int(window), float(scale), int(bool(sink)), sink_ptr, bias_ptr,
-                                                    dist_max, stream),
+                                                    dist_max, float(softcap), value_heads, stream),
                   "attention_sink_decode_bf16")
         return out
     return ops.attention_sink_generic(q, k_pages, v_pages, out, ctx.positions, ctx.token_req, table, cache.page_size, num_heads,
-                                      num_kv_heads, key_dim, value_dim, window, scale, sink, sink_logit=sink_logit, dist_bias=dist_bias)
+                                      num_kv_heads, key_dim, value_dim, window, scale, sink, sink_logit=sink_logit, dist_bias=dist_bias,
+                                      softcap=softcap, value_heads=value_heads, value_row=value_row)

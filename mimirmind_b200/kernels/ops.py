@@ -751,11 +751,17 @@ def qkv_pairs_post(qkv: torch.Tensor, q_out: torch.Tensor, k_pages: Optional[tor
 def attention_sink_generic(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, out: torch.Tensor, positions: torch.Tensor,
                            token_req: torch.Tensor, block_table: torch.Tensor, page_size: int, num_heads: int, num_kv_heads: int,
                            key_dim: int, value_dim: int, window: int, scale: float, sink: bool,
-                           sink_logit: Optional[torch.Tensor] = None, dist_bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+                           sink_logit: Optional[torch.Tensor] = None, dist_bias: Optional[torch.Tensor] = None, softcap: float = 0.0,
+                           value_heads: Optional[int] = None, value_row: Optional[int] = None) -> torch.Tensor:
     """Windowed causal attention of every token over its request's pages with keys of ``key_dim`` and values of
     ``value_dim``; with ``sink`` the softmax denominator has one added, with ``sink_logit`` (fp32 [heads]) the head's
     ``exp(logit)``; ``dist_bias`` (fp32 [heads, distances]) is added to the scaled score by distance, a head's last entry
-    standing for every larger distance (fp32 arithmetic, any sizes)."""
+    standing for every larger distance (fp32 arithmetic, any sizes).  ``softcap`` > 0: the scaled score becomes
+    ``cap * tanh(score / cap)``.  ``value_heads``: heads of the value pool (key head g reads value head g mod value_heads);
+    ``value_row``: numbers between the values of consecutive tokens (default ``value_dim``; larger when the values are the
+    leading part of a wider per-token array, which may be the key pool itself)."""
+    value_heads = num_kv_heads if value_heads is None else int(value_heads)
+    value_row = value_dim if value_row is None else int(value_row)
     _need(q, "attention q")
     n = q.shape[0]
     _need(out, "attention out", q.dtype)
@@ -763,7 +769,7 @@ def attention_sink_generic(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torc
     _need(v_pages, "attention v_pages", q.dtype)
     if q.shape != (n, num_heads * key_dim) or out.shape != (n, num_heads * value_dim):
         raise KernelError("attention: q/out shape mismatch")
-    if k_pages.shape[1:] != (num_kv_heads, page_size, key_dim) or v_pages.shape[1:] != (num_kv_heads, page_size, value_dim):
+    if k_pages.shape[1:] != (num_kv_heads, page_size, key_dim) or v_pages.shape[1:] != (value_heads, page_size, value_row):
         raise KernelError("attention: page pool shape mismatch")
     _need(positions, "positions", torch.int32)
     _need(token_req, "token_req", torch.int32)
@@ -780,7 +786,7 @@ def attention_sink_generic(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torc
         q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), out.data_ptr(), dtype_code(q.dtype), positions.data_ptr(),
         token_req.data_ptr(), block_table.data_ptr(), block_table.shape[1], page_size, n, num_heads, num_kv_heads, key_dim,
         value_dim, int(window), float(scale), int(bool(sink)), _ptr(sink_logit), _ptr(dist_bias),
-        dist_bias.shape[1] - 1 if dist_bias is not None else 0, _stream()), "attention_sink_generic")
+        dist_bias.shape[1] - 1 if dist_bias is not None else 0, float(softcap), value_heads, value_row, _stream()), "attention_sink_generic")
     return out
 
 
@@ -1181,4 +1187,171 @@ def moe_combine(y: torch.Tensor, wts: torch.Tensor, out_dtype: torch.dtype, plac
     out = torch.empty((n, d), dtype=out_dtype, device=y.device)
     check(_lib.load().mm_moe_combine(y.data_ptr(), dtype_code(y.dtype), wts.data_ptr(), _ptr(place), out.data_ptr(), dtype_code(out_dtype), n, top, d,
                                      _stream()), "moe_combine")
+    return out
+
+
+# ---- residual connections over several streams (csrc/hyper_connections.cu) ---------------------------------------------
+def stream_copies(x: torch.Tensor, streams: int) -> torch.Tensor:
+    """fp32 [n, D] -> fp32 [n, streams * D]: every stream starts as a copy of the row."""
+    _need(x, "stream copies", torch.float32)
+    n, d = x.shape
+    out = torch.empty((n, streams * d), dtype=torch.float32, device=x.device)
+    check(_lib.load().mm_stream_copies(x.data_ptr(), out.data_ptr(), n, int(streams), d, _stream()), "stream_copies")
+    return out
+
+
+def hc_read(x: torch.Tensor, streams: int, a: torch.Tensor, norm_weight: Optional[torch.Tensor], eps: float, out_dtype: torch.dtype,
+            rows: Optional[torch.Tensor] = None, n_rows: Optional[int] = None) -> torch.Tensor:
+    """``u = sum_s a[s] x_s`` over the streams of ``x`` (fp32 [n, streams * D]) and, with ``norm_weight``, its RMS norm
+    ``u w / sqrt(mean(u^2) + eps)``; with ``rows`` output row i is made from source row rows[i]."""
+    _need(x, "streams", torch.float32)
+    _need(a, "stream weights", torch.float32)
+    n, d = x.shape[0], x.shape[1] // streams
+    if x.shape[1] != streams * d or a.numel() != streams:
+        raise KernelError("stream read: shape mismatch")
+    if norm_weight is not None:
+        _need(norm_weight, "norm weight")
+        if norm_weight.numel() != d:
+            raise KernelError("stream read: the norm weight has another width")
+    if rows is not None:
+        _need(rows, "rows", torch.int32)
+        n = int(n_rows) if n_rows is not None else rows.numel()
+    out = torch.empty((n, d), dtype=out_dtype, device=x.device)
+    check(_lib.load().mm_hc_read(x.data_ptr(), _ptr(rows), a.data_ptr(), _ptr(norm_weight),
+                                 dtype_code(norm_weight.dtype) if norm_weight is not None else F32, float(eps), out.data_ptr(),
+                                 dtype_code(out_dtype), n, int(streams), d, _stream()), "hc_read")
+    return out
+
+
+def hc_write(x: torch.Tensor, streams: int, y: torch.Tensor, scale: Optional[torch.Tensor], mix: torch.Tensor, b: torch.Tensor,
+             a_next: Optional[torch.Tensor] = None, norm_weight: Optional[torch.Tensor] = None, eps: float = 0.0,
+             out_dtype: Optional[torch.dtype] = None) -> Optional[torch.Tensor]:
+    """All streams at once from the old ones, in place: ``x_t <- sum_s mix[s, t] x_s + b[t] (scale . y)``.  With ``a_next``
+    the next sublayer's input ``sum_t a_next[t] x_t`` (RMS-normed with ``norm_weight`` if given) comes out of the same pass."""
+    _need(x, "streams", torch.float32)
+    _need(y, "branch")
+    _need(mix, "stream mix", torch.float32)
+    _need(b, "stream out", torch.float32)
+    n, d = x.shape[0], x.shape[1] // streams
+    if x.shape[1] != streams * d or y.shape != (n, d) or mix.numel() != streams * streams or b.numel() != streams:
+        raise KernelError("stream write: shape mismatch")
+    if scale is not None:
+        _need(scale, "layer scale", torch.float32)
+        if scale.numel() != d:
+            raise KernelError("stream write: the layer scale has another width")
+    out = None
+    if a_next is not None:
+        _need(a_next, "stream weights", torch.float32)
+        if a_next.numel() != streams:
+            raise KernelError("stream write: shape mismatch")
+        if norm_weight is not None:
+            _need(norm_weight, "norm weight")
+        out = torch.empty((n, d), dtype=out_dtype or y.dtype, device=x.device)
+    check(_lib.load().mm_hc_write(x.data_ptr(), y.data_ptr(), dtype_code(y.dtype), _ptr(scale), mix.data_ptr(), b.data_ptr(), _ptr(a_next),
+                                  _ptr(norm_weight) if a_next is not None else None,
+                                  dtype_code(norm_weight.dtype) if norm_weight is not None else F32, float(eps), _ptr(out),
+                                  dtype_code(out.dtype) if out is not None else F32, n, int(streams), d, _stream()), "hc_write")
+    return out
+
+
+# ---- steps around an attention kernel (csrc/attention_parts.cu) --------------------------------------------------------
+def rope_half_table(positions: torch.Tensor, f_hi: torch.Tensor, f_lo: torch.Tensor) -> torch.Tensor:
+    """(cos, sin) of ``position * (f_hi[i] + f_lo[i])`` as fp32 [n, len(f_hi), 2]; the two words of each frequency come from
+    its float64 value, and the rounding of the product is carried, so the angle is good to the last bit of an fp32."""
+    _need(positions, "positions", torch.int32)
+    _need(f_hi, "frequencies", torch.float32)
+    _need(f_lo, "frequencies", torch.float32)
+    n, half = positions.numel(), f_hi.numel()
+    if f_lo.numel() != half or half < 1:
+        raise KernelError("rotation table: bad sizes")
+    out = torch.empty((n, half, 2), dtype=torch.float32, device=positions.device)
+    check(_lib.load().mm_rope_half_table(positions.data_ptr(), f_hi.data_ptr(), f_lo.data_ptr(), out.data_ptr(), n, half, _stream()), "rope_half_table")
+    return out
+
+
+def qkv_split_post(rows: torch.Tensor, q_off: int, k_off: int, v_off: int, q_out: torch.Tensor, k_pages: Optional[torch.Tensor],
+                   v_pages: Optional[torch.Tensor], slots: Optional[torch.Tensor], page_size: int, q_heads: int, k_heads: int, key_dim: int,
+                   v_heads: int, value_dim: int) -> None:
+    """Cuts fp32 rows [n, ld] into queries (``q_heads * key_dim`` numbers at ``q_off``, written to ``q_out``), keys
+    (``k_heads * key_dim`` at ``k_off``) and values (``v_heads * value_dim`` at ``v_off``), the last two written into
+    their pages ``[pages, heads, page_size, size]`` at ``slots``."""
+    if rows.dtype != torch.float32 or not rows.is_cuda or rows.stride(1) != 1:
+        raise KernelError("qkv split: fp32 rows with unit column stride are needed")
+    n = rows.shape[0]
+    _need(q_out, "q_out")
+    if q_out.shape != (n, q_heads * key_dim):
+        raise KernelError("qkv split: q_out has another shape")
+    if k_pages is not None:
+        _need(k_pages, "k_pages", q_out.dtype)
+        _need(v_pages, "v_pages", q_out.dtype)
+        _need(slots, "slots", torch.int32)
+        if k_pages.shape[1:] != (k_heads, page_size, key_dim) or v_pages.shape[1:] != (v_heads, page_size, value_dim):
+            raise KernelError("qkv split: page pool shape mismatch")
+    check(_lib.load().mm_qkv_split_post(rows.data_ptr(), rows.stride(0), int(q_off), int(k_off), int(v_off), q_out.data_ptr(), _ptr(k_pages),
+                                        _ptr(v_pages), dtype_code(q_out.dtype), _ptr(slots) if k_pages is not None else None, int(page_size), n,
+                                        int(q_heads), int(k_heads), int(key_dim), int(v_heads), int(value_dim), _stream()), "qkv_split_post")
+
+
+def latent_prep(rows: torch.Tensor, q_off: int, c_off: int, norm_weight: torch.Tensor, eps: float, rot: Optional[torch.Tensor], rot_dims: int,
+                q_plain: torch.Tensor, q_full: torch.Tensor, pages: Optional[torch.Tensor], slots: Optional[torch.Tensor], page_size: int,
+                heads: int, dim: int, rot_dim: int, rank: int) -> None:
+    """Between the projections of a latent attention and its kernel: from fp32 rows [n, ld] (every head's ``dim`` plain and
+    ``rot_dim`` rotated query numbers at ``q_off``; the latent's ``rank`` numbers and the shared key part's ``rot_dim`` at
+    ``c_off``) the plain query parts go to ``q_plain`` [n, heads * dim], the turned ones into ``q_full``
+    [n, heads, rank + rot_dim] behind each head's first ``rank`` places, and (normed latent, turned key part) into the
+    pages [pages, 1, page_size, rank + rot_dim] at ``slots``."""
+    if rows.dtype != torch.float32 or not rows.is_cuda or rows.stride(1) != 1:
+        raise KernelError("latent prep: fp32 rows with unit column stride are needed")
+    n = rows.shape[0]
+    _need(q_plain, "q_plain")
+    _need(q_full, "q_full", q_plain.dtype)
+    _need(norm_weight, "latent norm weight")
+    if q_plain.shape != (n, heads * dim) or q_full.shape != (n, heads * (rank + rot_dim)) or norm_weight.numel() != rank:
+        raise KernelError("latent prep: shape mismatch")
+    if rot_dims:
+        _need(rot, "rotation table", torch.float32)
+        if rot.shape != (n, rot_dims // 2, 2):
+            raise KernelError("latent prep: rotation table of another shape")
+    if pages is not None:
+        _need(pages, "latent pages", q_plain.dtype)
+        _need(slots, "slots", torch.int32)
+        if pages.shape[1:] != (1, page_size, rank + rot_dim):
+            raise KernelError("latent prep: page pool shape mismatch")
+    check(_lib.load().mm_latent_prep(rows.data_ptr(), rows.stride(0), int(q_off), int(c_off), norm_weight.data_ptr(), dtype_code(norm_weight.dtype),
+                                     float(eps), _ptr(rot) if rot_dims else None, int(rot_dims), q_plain.data_ptr(), q_full.data_ptr(), _ptr(pages),
+                                     dtype_code(q_plain.dtype), _ptr(slots) if pages is not None else None, int(page_size), n, int(heads), int(dim),
+                                     int(rot_dim), int(rank), _stream()), "latent_prep")
+
+
+def head_matmul(x: torch.Tensor, matrices: torch.Tensor, out: torch.Tensor, heads: int) -> torch.Tensor:
+    """``out[t, h, :] = x[t, h, :] . matrices[h]`` with ``matrices`` [heads, K, N]; ``x`` is [n, heads * K] and ``out``
+    [n, heads * N'] with N' >= N (each head's result goes to the first N places of its N' wide part); both may be column
+    slices of wider rows."""
+    H, K, N = matrices.shape
+    n = x.shape[0]
+    if H != heads or x.shape[1] != H * K or out.shape[0] != n or out.shape[1] % H or out.shape[1] // H < N:
+        raise KernelError("head product: shape mismatch")
+    if x.dtype != matrices.dtype or out.dtype != x.dtype or not matrices.is_contiguous() or x.stride(1) != 1 or out.stride(1) != 1:
+        raise KernelError("head product: one dtype and unit column strides are needed")
+    check(_lib.load().mm_head_matmul(x.data_ptr(), x.stride(0), K, matrices.data_ptr(), out.data_ptr(), out.stride(0), out.shape[1] // H,
+                                     dtype_code(x.dtype), n, H, K, N, _stream()), "head_matmul")
+    return out
+
+
+def head_finish(att: torch.Tensor, heads: int, value_dim: int, *, pair: bool = False, lam: float = 0.0, eps: Optional[float] = None,
+                post: float = 1.0, gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Per (token, head) of an attention output ``att`` [n, heads_in * value_dim] (``pair``: heads_in = 2 * heads and head h's
+    second map is head ``heads + h``): ``o = a1 - lam * a2``; with ``eps`` ``o / sqrt(mean(o^2) + eps)``; times ``post`` and
+    ``sigmoid(gate[t, h])`` (``gate`` fp32 [n, >= heads], may be a column slice).  Returns [n, heads * value_dim]."""
+    _need(att, "attention output")
+    n = att.shape[0]
+    heads_in = 2 * heads if pair else heads
+    if att.shape != (n, heads_in * value_dim):
+        raise KernelError("head finish: shape mismatch")
+    if gate is not None and (gate.dtype != torch.float32 or not gate.is_cuda or gate.stride(1) != 1 or gate.shape[0] != n or gate.shape[1] < heads):
+        raise KernelError("head finish: the gate is fp32 [n, heads] with unit column stride")
+    out = torch.empty((n, heads * value_dim), dtype=att.dtype, device=att.device)
+    check(_lib.load().mm_head_finish(att.data_ptr(), heads_in, heads if pair else 0, float(lam), int(eps is not None), float(eps or 0.0), float(post),
+                                     _ptr(gate), gate.stride(0) if gate is not None else 0, out.data_ptr(), dtype_code(att.dtype), n, int(heads),
+                                     int(value_dim), _stream()), "head_finish")
     return out

@@ -159,6 +159,51 @@ class ParallelBranchesBlock(Block):
         return out
 
 
+@BLOCKS.register("stream_connections")
+class StreamConnectionsBlock(Block):
+    """Pre-norm sublayers whose way in and out of the residual stream is a part of its own (``parts/connections.py``):
+    ``h = norm1(read1(x)); x <- write1(x, mixer(h)); h = norm2(read2(x)); x <- write2(x, ffn(h))``, with one or several
+    copies of the residual stream per token.  The connections are the layer's extra parts ``mixer_connection`` and
+    ``ffn_connection``; a layer whose feed-forward is of kind ``none`` has the first sublayer only.
+
+    A write and the read and norm that follow it are one launch, also across the border to the next block of this
+    kind, which gets its first normed rows as ``NormedRows``.  The streams are complete when the block returns."""
+
+    def __init__(self, *args, **kwargs):
+        super().__init__(*args, **kwargs)
+        from .mlp import NoFeedForward
+        self.has_ffn = not isinstance(self.feed_forward, NoFeedForward)
+        for name in ("mixer_connection",) + (("ffn_connection",) if self.has_ffn else ()):
+            if name not in self.extras:
+                raise ValueError(f"stream_connections block: the layer has no '{name}'")
+        self.mixer_connection = self.extras["mixer_connection"]
+        self.ffn_connection = self.extras.get("ffn_connection")
+
+    def forward(self, residual: torch.Tensor, pending, ctx: StepContext, cache: LayerCache,
+                successor: Optional[Block] = None):
+        dump = ctx.dump or (lambda stage, t: None)
+        first = self.mixer_connection
+        h = pending.x if isinstance(pending, NormedRows) else first.read(residual, self.mixer_norm)
+        dump("attn_norm", h)
+        branch = self.mixer.forward(h, ctx, cache)
+        dump("attn_out", branch)
+        last = first
+        if self.has_ffn:
+            h = first.write(residual, branch, self.ffn_connection, self.ffn_norm)
+            branch = self.feed_forward.forward(h, ctx)
+            dump("ffn_mlp", branch)
+            last = self.ffn_connection
+        made = None
+        if (isinstance(successor, StreamConnectionsBlock) and successor.mixer_connection.streams == last.streams
+                and successor.mixer_norm.factors() is not None and not ctx.plain_only):
+            made = last.write(residual, branch, successor.mixer_connection, successor.mixer_norm)
+        else:
+            last.write(residual, branch)
+        if ctx.dump is not None:
+            dump("l_out", last.total(residual))
+        return NormedRows(made) if made is not None else None
+
+
 def ops_add(residual: torch.Tensor, delta: torch.Tensor) -> None:
     from ..kernels import ops
     ops.add_residual(residual, delta)

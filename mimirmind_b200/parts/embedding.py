@@ -21,7 +21,8 @@ from .linear import linear
 
 @EMBEDDINGS.register("token_embedding")
 class TokenEmbedding(Embedding):
-    """spec params: vocab, width, scale, weight (full tensor name)."""
+    """spec params: vocab, width, scale, weight (full tensor name), copies (default 1: how many residual streams the
+    model keeps per token; each starts as a copy of the row, side by side in ``[n, copies * width]``)."""
 
     @classmethod
     def tensor_specs(cls, spec: PartSpec, prefix: str) -> List[TensorSpec]:
@@ -32,16 +33,18 @@ class TokenEmbedding(Embedding):
         self.vocab = int(spec["vocab"])
         self.width = int(spec["width"])
         self.scale = float(spec.get("scale", 1.0))
+        self.copies = int(spec.get("copies", 1) or 1)
         self.table = weights.get(spec["weight"]).contiguous()
 
     def native(self):
-        if type(self) is not TokenEmbedding:
+        if type(self) is not TokenEmbedding or self.copies != 1:
             return None
         return NativeDesc("token_embedding", {"vocab": self.vocab, "width": self.width, "scale": self.scale}, {"table": self.table})
 
     def forward(self, token_ids: torch.Tensor) -> torch.Tensor:
         out = torch.empty((token_ids.numel(), self.width), dtype=torch.float32, device=token_ids.device)
-        return ops.embedding(token_ids, self.table, out, self.scale)
+        ops.embedding(token_ids, self.table, out, self.scale)
+        return ops.stream_copies(out, self.copies) if self.copies > 1 else out
 
 
 @EMBEDDINGS.register("bigram_embedding")

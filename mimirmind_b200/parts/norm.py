@@ -20,7 +20,8 @@ from .base import NativeDesc, Norm, Runtime, WeightView
 @NORMS.register("rmsnorm")
 class RMSNorm(Norm):
     """spec params: width, eps, weight (tensor name under the prefix), offset (default 0: the stored weight multiplies
-    directly; 1: the weight is stored around zero and ``1 + w`` multiplies, formed once at load in fp32)."""
+    directly; 1: the weight is stored around zero and ``1 + w`` multiplies, formed once at load in fp32), streams (default
+    1; S: the residual holds S streams per token, ``[n, S * width]``, and the norm is taken of their sum)."""
 
     @classmethod
     def tensor_specs(cls, spec: PartSpec, prefix: str) -> List[TensorSpec]:
@@ -31,24 +32,30 @@ class RMSNorm(Norm):
         self.width = int(spec["width"])
         self.eps = float(spec["eps"])
         self.offset = float(spec.get("offset", 0.0))
+        self.streams = int(spec.get("streams", 1) or 1)
         self.weight = weights.get(spec["weight"]).contiguous()
         if self.offset:
             self.weight = (self.weight.float() + self.offset).contiguous()
+        self._ones = torch.ones(self.streams, dtype=torch.float32, device=rt.device) if self.streams > 1 else None
 
     def factors(self):
-        return self.weight, self.eps
+        return (self.weight, self.eps) if self.streams == 1 else None
 
     def native(self):
-        if type(self) is not RMSNorm or self.offset:
+        if type(self) is not RMSNorm or self.offset or self.streams != 1:
             return None
         return NativeDesc("rmsnorm", {"width": self.width, "eps": self.eps}, {"weight": self.weight})
 
     def forward(self, residual: torch.Tensor, delta: Optional[torch.Tensor], rows: Optional[torch.Tensor] = None,
                 n_rows: Optional[int] = None) -> torch.Tensor:
         n = residual.shape[0] if rows is None else (n_rows if n_rows is not None else rows.numel())
-        out = torch.empty((n, self.width), dtype=self.rt.dtype, device=residual.device)
         if rows is not None and rows.numel() != n:
             rows = rows[:n]
+        if self.streams > 1:
+            if delta is not None:
+                raise ValueError("rmsnorm over several streams: nothing can be pending, the streams are complete")
+            return ops.hc_read(residual, self.streams, self._ones, self.weight, self.eps, self.rt.dtype, rows, n if rows is not None else None)
+        out = torch.empty((n, self.width), dtype=self.rt.dtype, device=residual.device)
         return ops.add_rmsnorm(residual, delta, self.weight, self.eps, out, rows)
 
 

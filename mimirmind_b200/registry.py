@@ -4,7 +4,7 @@ The reference maps an architecture string to a backend object in one switch and
 fails naming the string when it is unknown (src/runtime/arch/ArchBackend.cpp:14-55;
 src/runtime/InferenceEngine.cpp:1321-1328), with a pure-name predicate for tests
 (src/runtime/arch/ArchBackend.hpp:231-235).  Here both levels are open tables so that
-another mixer, feed-forward, norm, position encoding, block arrangement or whole
+another mixer, feed-forward, norm, position encoding, block arrangement, residual connection or whole
 architecture is added by registering it, not by editing engine files.
 """
 from __future__ import annotations
@@ -60,9 +60,10 @@ POSITION_ENCODINGS = _Table("position encoding")
 BLOCKS = _Table("block arrangement")
 EMBEDDINGS = _Table("embedding")
 HEADS = _Table("output head")
+CONNECTIONS = _Table("residual connection")
 # the tables by the category a PartSpec may name (a layer's extra parts say which table holds their kind)
 CATEGORIES = {"mixer": MIXERS, "feed_forward": FEED_FORWARDS, "norm": NORMS, "position": POSITION_ENCODINGS, "block": BLOCKS,
-              "embedding": EMBEDDINGS, "head": HEADS}
+              "embedding": EMBEDDINGS, "head": HEADS, "connection": CONNECTIONS}
 
 
 def part_class(spec) -> Any:
@@ -117,4 +118,4 @@ def _ensure_builtin() -> None:
         return
     _builtin_loaded = True
     from . import parts  # noqa: F401  (registers part kinds)
-    from .models import bigerax, domelix, qwen2  # noqa: F401  (register the architectures)
+    from .models import bigerax, domelix, qwen2, tupunex  # noqa: F401  (register the architectures)

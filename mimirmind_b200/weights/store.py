@@ -139,6 +139,10 @@ def random_tensors(spec: ModelSpec, seed: int, dtype: torch.dtype, device="cpu")
             x = 0.2 * x
         elif ts.role == "bias":
             x = BIAS_STD * x
+        elif ts.role == "stream_read":    # how a sublayer reads several residual streams: near their mean
+            x = 1.0 / ts.shape[0] + 0.05 * x
+        elif ts.role == "stream_mix":     # how the streams are carried on: near the identity
+            x = torch.eye(ts.shape[0], device=device) + 0.05 * x
         elif ts.role == "mix":
             x = (0.5 + MIX_STD * x).clamp(0.05, 0.95)
         else:
