@@ -221,7 +221,7 @@ def forward(cfg: dict, weights: Dict[str, np.ndarray], tokens: List[int], layers
     """Logits [T, vocab] of a whole sequence; ``layers_out`` collects the residual stream (the sum of the streams) after
     every layer run."""
     eps = cfg["norm"]["eps"]
-    x = weights["embed"][np.asarray(tokens)] * cfg["embedding"]["scale"]
+    x = weights["embed"][np.asarray(tokens)] * (cfg.get("embedding") or {}).get("scale", 1.0)
     S = cfg.get("streams")
     streams = np.stack([x] * S) if S else None
     for i in layer_order(cfg):
