@@ -221,9 +221,9 @@ MM_EXPORT int mm_head_matmul(const void* in, long long in_ld, int in_hs, const v
 // ---------------------------------------------------------------------------------------------------------------
 // att [n, heads_in, dv]; with pair > 0 head h's second map is head h + pair of the same token.  One warp per (token, head):
 //   o = a1 - lambda a2;  normalize: o <- o / sqrt(mean(o^2) + eps);  o <- o * post * sigmoid(gate[t * ldg + h])
-template <typename T>
+template <typename T, typename TO = T>
 __global__ void head_finish_kernel(const T* __restrict__ att, int heads_in, int pair, float lambda, int normalize, float eps, float post,
-                                   const float* __restrict__ gate, int ldg, T* __restrict__ out, int n_tokens, int H, int dv) {
+                                   const float* __restrict__ gate, int ldg, TO* __restrict__ out, int n_tokens, int H, int dv) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + warp;
     if (item >= (long long)n_tokens * H) return;
@@ -240,22 +240,26 @@ __global__ void head_finish_kernel(const T* __restrict__ att, int heads_in, int 
         factor *= rsqrtf(warp_sum(sq) / (float)dv + eps);
     }
     if (gate != nullptr) factor *= 1.0f / (1.0f + expf(-gate[(size_t)t * ldg + h]));
-    T* o_row = out + ((size_t)t * H + h) * dv;
+    TO* o_row = out + ((size_t)t * H + h) * dv;
     for (int d = lane; d < dv; d += 32) {
         const float o = pair ? fmaf(-lambda, to_f32<T>(a2[d]), to_f32<T>(a1[d])) : to_f32<T>(a1[d]);
-        o_row[d] = from_f32<T>(o * factor);
+        o_row[d] = from_f32<TO>(o * factor);
     }
 }
 
 MM_EXPORT int mm_head_finish(const void* att, int heads_in, int pair, float lambda, int normalize, float eps, float post, const void* gate, int ldg,
-                             void* out, int dtype, int n_tokens, int H, int dv, void* stream) {
+                             void* out, int dtype, int out_dtype, int n_tokens, int H, int dv, void* stream) {
     MM_REQUIRE(n_tokens >= 0 && H > 0 && dv > 0 && pair >= 0 && heads_in >= H + pair, "head finish: bad sizes");
     MM_REQUIRE(gate == nullptr || ldg >= H, "head finish: one gate per head");
     if (n_tokens == 0) return MM_OK;
     cudaStream_t s = (cudaStream_t)stream;
     const long long items = (long long)n_tokens * H;
     const int blocks = ceil_div(items, 4);
-    if (dtype == MM_F32)
+    MM_REQUIRE(out_dtype == dtype || dtype == MM_F32, "head finish: only an fp32 input can be given out in another type");
+    if (dtype == MM_F32 && out_dtype == MM_BF16)
+        mm_launch(head_finish_kernel<float, __nv_bfloat16>, dim3(blocks), dim3(128), 0, s, (const float*)att, heads_in, pair, lambda, normalize,
+                  eps, post, (const float*)gate, ldg, (__nv_bfloat16*)out, n_tokens, H, dv);
+    else if (dtype == MM_F32)
         mm_launch(head_finish_kernel<float>, dim3(blocks), dim3(128), 0, s, (const float*)att, heads_in, pair, lambda, normalize, eps, post,
                   (const float*)gate, ldg, (float*)out, n_tokens, H, dv);
     else if (dtype == MM_BF16)

@@ -180,9 +180,9 @@ MM_EXPORT int mm_qkv_pairs_post(const void* qkv, void* q_out, void* k_pages, voi
 // ---------------------------------------------------------------------------------------------------------------
 #define SINK_MAX_ACC 16  // dv <= 512
 
-template <typename T>
+template <typename T, typename TO = T>
 __global__ void attention_sink_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_pages,
-                                              const T* __restrict__ v_pages, T* __restrict__ out,
+                                              const T* __restrict__ v_pages, TO* __restrict__ out,
                                               const int32_t* __restrict__ positions, const int32_t* __restrict__ token_req,
                                               const int32_t* __restrict__ block_table, int table_width, int page_size,
                                               int n_tokens, int H, int G, int dk, int dv, int window, float scale, int sink,
@@ -250,11 +250,11 @@ __global__ void attention_sink_generic_kernel(const T* __restrict__ q, const T* 
         m = m_new;
     }
     const float inv_l = (l > 0.0f) ? 1.0f / l : 0.0f;
-    T* orow = out + ((size_t)t * H + h) * dv;
+    TO* orow = out + ((size_t)t * H + h) * dv;
 #pragma unroll
     for (int a = 0; a < SINK_MAX_ACC; ++a) {
         const int d = a * 32 + lane;
-        if (d < dv) orow[d] = from_f32<T>(acc[a] * inv_l);
+        if (d < dv) orow[d] = from_f32<TO>(acc[a] * inv_l);
     }
 }
 
@@ -262,7 +262,7 @@ MM_EXPORT int mm_attention_sink_generic(const void* q, const void* k_pages, cons
                                         const void* positions, const void* token_req, const void* block_table,
                                         int table_width, int page_size, int n_tokens, int H, int G, int dk, int dv, int window,
                                         float scale, int sink, const void* sink_logit, const void* dist_bias, int dist_max, float softcap,
-                                        int Gv, int v_row, void* stream) {
+                                        int Gv, int v_row, int out_f32, void* stream) {
     MM_REQUIRE(dist_bias == nullptr || dist_max >= 0, "attention: the distance table needs at least one row");
     MM_REQUIRE(Gv >= 1 && G % Gv == 0 && v_row >= dv && softcap >= 0.0f, "attention: value heads must divide the key heads, a value row holds at least dv numbers");
     MM_REQUIRE(n_tokens >= 0 && H > 0 && G > 0 && dk > 0 && dv > 0 && H % G == 0, "attention: heads must be a positive multiple of kv heads");
@@ -279,6 +279,11 @@ MM_EXPORT int mm_attention_sink_generic(const void* q, const void* k_pages, cons
                   (const float*)v_pages, (float*)out, (const int32_t*)positions, (const int32_t*)token_req,
                   (const int32_t*)block_table, table_width, page_size, n_tokens, H, G, dk, dv, window, scale, sink,
                   (const float*)sink_logit, (const float*)dist_bias, dist_max, softcap, Gv, v_row);
+    else if (dtype == MM_BF16 && out_f32)      // the result is not rounded: what follows takes a difference of heads
+        mm_launch(attention_sink_generic_kernel<__nv_bfloat16, float>, dim3(blocks), dim3(warps * 32), smem, s, (const __nv_bfloat16*)q,
+                  (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, (float*)out, (const int32_t*)positions,
+                  (const int32_t*)token_req, (const int32_t*)block_table, table_width, page_size, n_tokens, H, G, dk, dv, window,
+                  scale, sink, (const float*)sink_logit, (const float*)dist_bias, dist_max, softcap, Gv, v_row);
     else if (dtype == MM_BF16)
         mm_launch(attention_sink_generic_kernel<__nv_bfloat16>, dim3(blocks), dim3(warps * 32), smem, s, (const __nv_bfloat16*)q,
                   (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, (__nv_bfloat16*)out, (const int32_t*)positions,

@@ -65,7 +65,8 @@ __device__ __forceinline__ void load_kv_tile2(__nv_bfloat16* dK, __nv_bfloat16* 
 template <int DK, int DV>
 __global__ void __launch_bounds__(SATT_THREADS) attention_sink_prefill_kernel(
     const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_pages,
-    const __nv_bfloat16* __restrict__ v_pages, __nv_bfloat16* __restrict__ out, const int32_t* __restrict__ tiles,
+    const __nv_bfloat16* __restrict__ v_pages, __nv_bfloat16* __restrict__ out, float* __restrict__ out32,
+    const int32_t* __restrict__ tiles,
     const int32_t* __restrict__ block_table, int table_width, int page_size, int H, int G, int window, float scale_log2,
     int sink, const float* __restrict__ sink_logit, const float* __restrict__ dist_bias, int dist_max, float softcap, int Gv) {
     constexpr int KS = DK + 8, VS = DV + 8;
@@ -246,10 +247,14 @@ __global__ void __launch_bounds__(SATT_THREADS) attention_sink_prefill_kernel(
 #pragma unroll
     for (int j = 0; j < NT_O; ++j) {
         const int col = j * 8 + (lane & 3) * 2;
-        if (valid_lo)
-            *reinterpret_cast<uint32_t*>(out + ((size_t)(row0 + r_lo) * H + h) * DV + col) = pack_bf16(o[j][0] * inv_lo, o[j][1] * inv_lo);
-        if (valid_hi)
-            *reinterpret_cast<uint32_t*>(out + ((size_t)(row0 + r_hi) * H + h) * DV + col) = pack_bf16(o[j][2] * inv_hi, o[j][3] * inv_hi);
+        const size_t at_lo = ((size_t)(row0 + r_lo) * H + h) * DV + col, at_hi = ((size_t)(row0 + r_hi) * H + h) * DV + col;
+        if (out32 != nullptr) {
+            if (valid_lo) *reinterpret_cast<float2*>(out32 + at_lo) = make_float2(o[j][0] * inv_lo, o[j][1] * inv_lo);
+            if (valid_hi) *reinterpret_cast<float2*>(out32 + at_hi) = make_float2(o[j][2] * inv_hi, o[j][3] * inv_hi);
+        } else {
+            if (valid_lo) *reinterpret_cast<uint32_t*>(out + at_lo) = pack_bf16(o[j][0] * inv_lo, o[j][1] * inv_lo);
+            if (valid_hi) *reinterpret_cast<uint32_t*>(out + at_hi) = pack_bf16(o[j][2] * inv_hi, o[j][3] * inv_hi);
+        }
     }
 }
 
@@ -259,7 +264,7 @@ __global__ void __launch_bounds__(SATT_THREADS) attention_sink_prefill_kernel(
 template <int DK, int DV>
 __global__ void __launch_bounds__(SATT_THREADS) attention_sink_decode_kernel(
     const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_pages,
-    const __nv_bfloat16* __restrict__ v_pages, __nv_bfloat16* __restrict__ out, float* __restrict__ part_o,
+    const __nv_bfloat16* __restrict__ v_pages, __nv_bfloat16* __restrict__ out, float* __restrict__ out32, float* __restrict__ part_o,
     float* __restrict__ part_ml, const int32_t* __restrict__ items,
     const int32_t* __restrict__ positions, const int32_t* __restrict__ token_req, const int32_t* __restrict__ block_table,
     int table_width, int page_size, int H, int G, int window, float scale_log2, int sink, const float* __restrict__ sink_logit,
@@ -439,7 +444,9 @@ __global__ void __launch_bounds__(SATT_THREADS) attention_sink_decode_kernel(
         }
         const int h = g * qpg + r;
         if (single) {
-            out[((size_t)t * H + h) * DV + col] = __float2bfloat16_rn(l > 0.0f ? acc / l : 0.0f);
+            const float res = l > 0.0f ? acc / l : 0.0f;
+            if (out32 != nullptr) out32[((size_t)t * H + h) * DV + col] = res;
+            else out[((size_t)t * H + h) * DV + col] = __float2bfloat16_rn(res);
         } else {
             const size_t p = ((size_t)item * H + h) * n_splits + split;
             part_o[p * DV + col] = acc;
@@ -452,7 +459,7 @@ __global__ void __launch_bounds__(SATT_THREADS) attention_sink_decode_kernel(
 }
 
 // The splits of every (item, head) put together in split order, with the sink's share: one block per (item, head).
-__global__ void attention_sink_merge_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict__ part_o,
+__global__ void attention_sink_merge_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ out32, const float* __restrict__ part_o,
                                             const float* __restrict__ part_ml, const int32_t* __restrict__ items, int H, int dv,
                                             int n_splits, int sink, const float* __restrict__ sink_logit) {
     const int item = blockIdx.x, h = blockIdx.y;
@@ -469,7 +476,8 @@ __global__ void attention_sink_merge_kernel(__nv_bfloat16* __restrict__ out, con
     for (int col = threadIdx.x; col < dv; col += blockDim.x) {
         float acc = 0.0f;
         for (int s = 0; s < n_splits; ++s) acc += part_o[(p0 + s) * dv + col] * exp2f(part_ml[(p0 + s) * 2] - mu);
-        out[((size_t)t * H + h) * dv + col] = __float2bfloat16_rn(acc * inv);
+        if (out32 != nullptr) out32[((size_t)t * H + h) * dv + col] = acc * inv;
+        else out[((size_t)t * H + h) * dv + col] = __float2bfloat16_rn(acc * inv);
     }
 }
 
@@ -478,7 +486,7 @@ static const float SINK_LOG2E = 1.4426950408889634f;
 template <int DK, int DV>
 static int launch_sink_prefill(const void* q, const void* k, const void* v, void* out, const void* tiles, int n_tiles,
                                const void* table, int table_width, int page_size, int H, int G, int window, float scale, int sink,
-                               const void* sink_logit, const void* dist_bias, int dist_max, float softcap, int Gv,
+                               const void* sink_logit, const void* dist_bias, int dist_max, float softcap, int Gv, int out_f32,
                                cudaStream_t s) {
     const size_t smem = (size_t)(3 * 64 * (DK + 8) + 2 * 64 * (DV + 8)) * sizeof(__nv_bfloat16);
     auto kernel = attention_sink_prefill_kernel<DK, DV>;
@@ -488,7 +496,8 @@ static int launch_sink_prefill(const void* q, const void* k, const void* v, void
         return MM_ERR_UNSUPPORTED;
     }
     mm_launch(kernel, dim3(H, n_tiles), dim3(SATT_THREADS), smem, s, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k,
-              (const __nv_bfloat16*)v, (__nv_bfloat16*)out, (const int32_t*)tiles, (const int32_t*)table, table_width, page_size, H, G,
+              (const __nv_bfloat16*)v, out_f32 ? nullptr : (__nv_bfloat16*)out, out_f32 ? (float*)out : nullptr, (const int32_t*)tiles,
+              (const int32_t*)table, table_width, page_size, H, G,
               window, scale * SINK_LOG2E, sink, (const float*)sink_logit, (const float*)dist_bias, dist_max, softcap, Gv);
     MM_CHECK_LAUNCH();
     return MM_OK;
@@ -499,7 +508,7 @@ static int launch_sink_decode(const void* q, const void* k, const void* v, void*
                               const void* items, int n_items,
                               const void* positions, const void* token_req, const void* table, int table_width, int page_size,
                               int H, int G, int window, float scale, int sink, const void* sink_logit, const void* dist_bias, int dist_max,
-                              float softcap, int Gv, cudaStream_t s) {
+                              float softcap, int Gv, int out_f32, cudaStream_t s) {
     const size_t kv = (size_t)SDEC_STAGES * 64 * (DK + 8 + DV + 8) * sizeof(__nv_bfloat16);
     const size_t merge = (size_t)(4 * 16 * DV + 4 * 16 * 2) * sizeof(float);
     const size_t smem = kv > merge ? kv : merge;
@@ -510,12 +519,14 @@ static int launch_sink_decode(const void* q, const void* k, const void* v, void*
         return MM_ERR_UNSUPPORTED;
     }
     mm_launch(kernel, dim3(n_items, G, n_splits), dim3(SATT_THREADS), smem, s, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k,
-              (const __nv_bfloat16*)v, (__nv_bfloat16*)out, (float*)part_o, (float*)part_ml, (const int32_t*)items,
+              (const __nv_bfloat16*)v, out_f32 ? nullptr : (__nv_bfloat16*)out, out_f32 ? (float*)out : nullptr, (float*)part_o,
+              (float*)part_ml, (const int32_t*)items,
               (const int32_t*)positions, (const int32_t*)token_req, (const int32_t*)table, table_width, page_size, H, G, window,
               scale * SINK_LOG2E, sink, (const float*)sink_logit, (const float*)dist_bias, dist_max, softcap, Gv);
     MM_CHECK_LAUNCH();
     if (n_splits > 1) {
-        mm_launch(attention_sink_merge_kernel, dim3(n_items, H), dim3(DV >= 64 ? 64 : 32), 0, s, (__nv_bfloat16*)out, (const float*)part_o,
+        mm_launch(attention_sink_merge_kernel, dim3(n_items, H), dim3(DV >= 64 ? 64 : 32), 0, s, out_f32 ? nullptr : (__nv_bfloat16*)out,
+                  out_f32 ? (float*)out : nullptr, (const float*)part_o,
                   (const float*)part_ml, (const int32_t*)items, H, DV, n_splits, sink, (const float*)sink_logit);
         MM_CHECK_LAUNCH();
     }
@@ -551,14 +562,14 @@ MM_EXPORT int mm_attention_sink_supported(int dk, int dv) {
 MM_EXPORT int mm_attention_sink_prefill_bf16(const void* q, const void* k_pages, const void* v_pages, void* out, const void* tiles,
                                              int n_tiles, const void* block_table, int table_width, int page_size, int H, int G,
                                              int dk, int dv, int window, float scale, int sink, const void* sink_logit, const void* dist_bias,
-                                             int dist_max, float softcap, int Gv, void* stream) {
+                                             int dist_max, float softcap, int Gv, int out_f32, void* stream) {
     MM_REQUIRE(Gv >= 1 && G % Gv == 0 && softcap >= 0.0f, "sink attention: the value heads must divide the key heads");
     MM_REQUIRE(n_tiles >= 0 && H > 0 && G > 0 && H % G == 0, "sink attention: heads must be a positive multiple of kv heads");
     MM_REQUIRE(page_size > 0 && table_width > 0 && window >= 0 && scale > 0.0f, "sink attention: bad page geometry, window or scale");
     if (n_tiles == 0) return MM_OK;
     cudaStream_t s = (cudaStream_t)stream;
     SINK_DISPATCH(launch_sink_prefill, q, k_pages, v_pages, out, tiles, n_tiles, block_table, table_width, page_size, H, G, window, scale,
-                  sink, sink_logit, dist_bias, dist_max, softcap, Gv, s);
+                  sink, sink_logit, dist_bias, dist_max, softcap, Gv, out_f32, s);
     mm_set_last_error("sink attention: key and value sizes must each be one of 32, 64, 96, 128");
     return MM_ERR_UNSUPPORTED;
 }
@@ -570,7 +581,7 @@ MM_EXPORT int mm_attention_sink_decode_bf16(const void* q, const void* k_pages, 
                                             int n_items, const void* positions, const void* token_req, const void* block_table,
                                             int table_width, int page_size, int H, int G, int dk, int dv, int window, float scale,
                                             int sink, const void* sink_logit, const void* dist_bias, int dist_max, float softcap, int Gv,
-                                            void* stream) {
+                                            int out_f32, void* stream) {
     MM_REQUIRE(Gv >= 1 && G % Gv == 0 && softcap >= 0.0f, "sink attention: the value heads must divide the key heads");
     MM_REQUIRE(n_splits >= 1 && n_splits <= 64 && (n_splits == 1 || (part_o != nullptr && part_ml != nullptr)),
                "sink attention: 1..64 splits, with scratch for more than one");
@@ -579,7 +590,7 @@ MM_EXPORT int mm_attention_sink_decode_bf16(const void* q, const void* k_pages, 
     if (n_items == 0) return MM_OK;
     cudaStream_t s = (cudaStream_t)stream;
     SINK_DISPATCH(launch_sink_decode, q, k_pages, v_pages, out, part_o, part_ml, n_splits, items, n_items, positions, token_req, block_table,
-                  table_width, page_size, H, G, window, scale, sink, sink_logit, dist_bias, dist_max, softcap, Gv, s);
+                  table_width, page_size, H, G, window, scale, sink, sink_logit, dist_bias, dist_max, softcap, Gv, out_f32, s);
     mm_set_last_error("sink attention: key and value sizes must each be one of 32, 64, 96, 128");
     return MM_ERR_UNSUPPORTED;
 }

@@ -38,8 +38,8 @@ def _sink_lib():
     if not _sink_declared:
         P, I, F = c_void_p, c_int, c_float
         _lib.declare("mm_attention_sink_supported", [I, I])
-        _lib.declare("mm_attention_sink_prefill_bf16", [P, P, P, P, P, I, P, I, I, I, I, I, I, I, F, I, P, P, I, F, I, P])
-        _lib.declare("mm_attention_sink_decode_bf16", [P, P, P, P, P, P, I, P, I, P, P, P, I, I, I, I, I, I, I, F, I, P, P, I, F, I, P])
+        _lib.declare("mm_attention_sink_prefill_bf16", [P, P, P, P, P, I, P, I, I, I, I, I, I, I, F, I, P, P, I, F, I, I, P])
+        _lib.declare("mm_attention_sink_decode_bf16", [P, P, P, P, P, P, I, P, I, P, P, P, I, I, I, I, I, I, I, F, I, P, P, I, F, I, I, P])
         _lib.declare("mm_attention_decode_tma_bf16_sink", [P, P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, I, I, P, P])
         _lib.declare("mm_attention_prefill_tcgen05_sink", [P, P, P, P, P, I, P, I, I, I, I, I, I, I, I, F, I, P, P])
         _sink_declared = True
@@ -103,7 +103,8 @@ def paged_sink_attention(q, cache, out, ctx, num_heads: int, num_kv_heads: int, 
     ``softcap`` > 0 bends the scaled score into ``cap * tanh(score / cap)``.  ``value_heads`` (a divisor of the key heads):
     the value pool has that many heads and key head ``g`` reads value head ``g mod value_heads`` (several key heads over one
     set of values).  ``k_pages`` / ``v_pages``: the pools, if they are not the cache's arrays ``k`` and ``v``; ``value_row``:
-    how many numbers lie between the values of consecutive tokens (values that are a slice of a wider per-token array)."""
+    how many numbers lie between the values of consecutive tokens (values that are a slice of a wider per-token array).
+    ``out`` may be fp32 beside bfloat16 queries: the result is then not rounded (what follows takes a difference of heads)."""
     table = cache.block_table
     k_pages = cache.arrays["k"] if k_pages is None else k_pages
     v_pages = cache.arrays["v"] if v_pages is None else v_pages
@@ -116,7 +117,8 @@ def paged_sink_attention(q, cache, out, ctx, num_heads: int, num_kv_heads: int, 
         # equal key and value sizes of 64 or 128: the tcgen05 prefill kernel of the plain attention, told of the sink
         from . import attention_bf16
         # a learned sink or a distance bias: the mma.sync kernels take them, the tcgen05 and TMA kernels do not
-        extended = sink_logit is not None or dist_bias is not None or softcap > 0 or value_heads != num_kv_heads
+        out_f32 = int(out.dtype == torch.float32)
+        extended = sink_logit is not None or dist_bias is not None or softcap > 0 or value_heads != num_kv_heads or bool(out_f32)
         sink_ptr = sink_logit.data_ptr() if sink_logit is not None else None
         bias_ptr = dist_bias.data_ptr() if dist_bias is not None else None
         dist_max = dist_bias.shape[1] - 1 if dist_bias is not None else 0
@@ -134,7 +136,7 @@ def paged_sink_attention(q, cache, out, ctx, num_heads: int, num_kv_heads: int, 
             check(lib.mm_attention_sink_prefill_bf16(q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), out.data_ptr(), tiles.data_ptr(),
                                                      n_tiles, table.data_ptr(), table.shape[1], cache.page_size, num_heads, num_kv_heads,
                                                      key_dim, value_dim, int(window), float(scale), int(bool(sink)), sink_ptr, bias_ptr, dist_max,
-                                                     float(softcap), value_heads, stream),
+                                                     float(softcap), value_heads, out_f32, stream),
                   "attention_sink_prefill_bf16")
         tma = None
         if n_items and USE_SINK_TMA_DECODE and not extended and key_dim == value_dim and key_dim in (64, 128) and cache.page_size in (8, 16, 32, 64):
@@ -166,7 +168,7 @@ def paged_sink_attention(q, cache, out, ctx, num_heads: int, num_kv_heads: int, 
                                                     items.data_ptr() if items is not None else None, n_items, ctx.positions.data_ptr(),
                                                     ctx.token_req.data_ptr(), table.data_ptr(), table.shape[1], cache.page_size, num_heads,
                                                     num_kv_heads, key_dim, value_dim, int(window), float(scale), int(bool(sink)), sink_ptr, bias_ptr,
-                                                    dist_max, float(softcap), value_heads, stream),
+                                                    dist_max, float(softcap), value_heads, out_f32, stream),
                   "attention_sink_decode_bf16")
         return out
     return ops.attention_sink_generic(q, k_pages, v_pages, out, ctx.positions, ctx.token_req, table, cache.page_size, num_heads,

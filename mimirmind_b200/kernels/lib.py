@@ -59,7 +59,7 @@ _PROTOTYPES = {
     "mm_embedding_bigram": [P, P, P, P, P, P, P, P, I, P, I, I, I, I, c_longlong, c_longlong, P],
     "mm_qkv_pairs_post": [P, P, P, P, P, I, P, P, I, I, I, I, I, I, I, I, F, P],
     "mm_rope_pairs_table": [P, P, P, I, I, P],
-    "mm_attention_sink_generic": [P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, I, F, I, P, P, I, F, I, I, P],
+    "mm_attention_sink_generic": [P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, I, F, I, P, P, I, F, I, I, I, P],
     "mm_mingru_walk": [P, P, I, P, P, P, P, P, I, I, P],
     "mm_mingru_chunked": [P, P, I, P, P, P, P, P, P, P, P, I, I, I, P],
     "mm_bias_act": [P, P, I, P, I, I, I, I, P],
@@ -83,7 +83,7 @@ _PROTOTYPES = {
     "mm_qkv_split_post": [P, I, I, I, I, P, P, P, I, P, I, I, I, I, I, I, I, P],
     "mm_latent_prep": [P, I, I, I, P, I, F, P, I, P, P, P, I, P, I, I, I, I, I, I, P],
     "mm_head_matmul": [P, c_longlong, I, P, P, c_longlong, I, I, I, I, I, I, P],
-    "mm_head_finish": [P, I, I, F, I, F, F, P, I, P, I, I, I, I, P],
+    "mm_head_finish": [P, I, I, F, I, F, F, P, I, P, I, I, I, I, I, P],
     "mm_gemm_tcgen05_grouped": [P, P, P, I, I, I, I, I, I, I, P, P, I, P, P],
 }
 

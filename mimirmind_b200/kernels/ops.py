@@ -759,12 +759,12 @@ def attention_sink_generic(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torc
     standing for every larger distance (fp32 arithmetic, any sizes).  ``softcap`` > 0: the scaled score becomes
     ``cap * tanh(score / cap)``.  ``value_heads``: heads of the value pool (key head g reads value head g mod value_heads);
     ``value_row``: numbers between the values of consecutive tokens (default ``value_dim``; larger when the values are the
-    leading part of a wider per-token array, which may be the key pool itself)."""
+    leading part of a wider per-token array, which may be the key pool itself).  ``out`` has q's type or is fp32."""
     value_heads = num_kv_heads if value_heads is None else int(value_heads)
     value_row = value_dim if value_row is None else int(value_row)
     _need(q, "attention q")
     n = q.shape[0]
-    _need(out, "attention out", q.dtype)
+    _need(out, "attention out", torch.float32 if out.dtype == torch.float32 else q.dtype)
     _need(k_pages, "attention k_pages", q.dtype)
     _need(v_pages, "attention v_pages", q.dtype)
     if q.shape != (n, num_heads * key_dim) or out.shape != (n, num_heads * value_dim):
@@ -786,7 +786,8 @@ def attention_sink_generic(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torc
         q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), out.data_ptr(), dtype_code(q.dtype), positions.data_ptr(),
         token_req.data_ptr(), block_table.data_ptr(), block_table.shape[1], page_size, n, num_heads, num_kv_heads, key_dim,
         value_dim, int(window), float(scale), int(bool(sink)), _ptr(sink_logit), _ptr(dist_bias),
-        dist_bias.shape[1] - 1 if dist_bias is not None else 0, float(softcap), value_heads, value_row, _stream()), "attention_sink_generic")
+        dist_bias.shape[1] - 1 if dist_bias is not None else 0, float(softcap), value_heads, value_row,
+        int(out.dtype == torch.float32 and q.dtype != torch.float32), _stream()), "attention_sink_generic")
     return out
 
 
@@ -1339,10 +1340,11 @@ def head_matmul(x: torch.Tensor, matrices: torch.Tensor, out: torch.Tensor, head
 
 
 def head_finish(att: torch.Tensor, heads: int, value_dim: int, *, pair: bool = False, lam: float = 0.0, eps: Optional[float] = None,
-                post: float = 1.0, gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+                post: float = 1.0, gate: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
     """Per (token, head) of an attention output ``att`` [n, heads_in * value_dim] (``pair``: heads_in = 2 * heads and head h's
     second map is head ``heads + h``): ``o = a1 - lam * a2``; with ``eps`` ``o / sqrt(mean(o^2) + eps)``; times ``post`` and
-    ``sigmoid(gate[t, h])`` (``gate`` fp32 [n, >= heads], may be a column slice).  Returns [n, heads * value_dim]."""
+    ``sigmoid(gate[t, h])`` (``gate`` fp32 [n, >= heads], may be a column slice).  Returns [n, heads * value_dim] of
+    ``out_dtype`` (default: that of ``att``; an fp32 ``att`` may be given out as bfloat16)."""
     _need(att, "attention output")
     n = att.shape[0]
     heads_in = 2 * heads if pair else heads
@@ -1350,8 +1352,12 @@ def head_finish(att: torch.Tensor, heads: int, value_dim: int, *, pair: bool = F
         raise KernelError("head finish: shape mismatch")
     if gate is not None and (gate.dtype != torch.float32 or not gate.is_cuda or gate.stride(1) != 1 or gate.shape[0] != n or gate.shape[1] < heads):
         raise KernelError("head finish: the gate is fp32 [n, heads] with unit column stride")
-    out = torch.empty((n, heads * value_dim), dtype=att.dtype, device=att.device)
+    out_dtype = out_dtype or att.dtype
+    if out_dtype != att.dtype and att.dtype != torch.float32:
+        raise KernelError("head finish: only an fp32 input can be given out in another type")
+    out = torch.empty((n, heads * value_dim), dtype=out_dtype, device=att.device)
     check(_lib.load().mm_head_finish(att.data_ptr(), heads_in, heads if pair else 0, float(lam), int(eps is not None), float(eps or 0.0), float(post),
-                                     _ptr(gate), gate.stride(0) if gate is not None else 0, out.data_ptr(), dtype_code(att.dtype), n, int(heads),
+                                     _ptr(gate), gate.stride(0) if gate is not None else 0, out.data_ptr(), dtype_code(att.dtype),
+                                     dtype_code(out_dtype), n, int(heads),
                                      int(value_dim), _stream()), "head_finish")
     return out

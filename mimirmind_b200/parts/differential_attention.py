@@ -127,10 +127,11 @@ class DifferentialAttention(Mixer):
             slots = ctx.derived[skey]
         q = torch.empty((n, 2 * H * dk), dtype=self.rt.dtype, device=a.device)
         ops.qkv_split_post(rows, 0, 2 * H * dk, 2 * (H + G) * dk, q, k_pages, v_pages, slots, cache.page_size, 2 * H, 2 * G, dk, G, dv)
-        att = torch.empty((n, 2 * H * dv), dtype=self.rt.dtype, device=a.device)
+        # both maps' results stay fp32: their difference is normed to unit size, which would magnify a rounding of the maps
+        att = torch.empty((n, 2 * H * dv), dtype=torch.float32, device=a.device)
         from ..kernels import attention as attn_kernels
         attn_kernels.paged_sink_attention(q, cache, att, ctx, 2 * H, 2 * G, dk, dv, self.window, self.scale, False,
                                           softcap=self.softcap, value_heads=G)
         o = ops.head_finish(att, H, dv, pair=True, lam=self.lam, eps=self.eps, post=1.0 - self.diff,
-                            gate=a[:, C:C + H] if self.has_gate else None)
+                            gate=a[:, C:C + H] if self.has_gate else None, out_dtype=self.rt.dtype)
         return linear(o, self.w_o, None, self.rt)
