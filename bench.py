@@ -166,7 +166,7 @@ def run_workload(name: str, layers: int) -> int:
     return 0 if verified else 1
 
 
-# ---- another design beside the closest existing one, at equal size (--compare bigerax | domelix) ---------------------------------------
+# ---- another design beside the closest existing one, at equal size (--compare bigerax | domelix | tupunex) ---------------------------------------
 # Layer sizes that resemble a real model's; both models get the same width, heads, key size, window, layer count and
 # vocabulary, and feed-forwards of equal parameter count (two matrices of ff against three of 2/3 ff).
 COMPARE_SIZES = {
@@ -201,6 +201,23 @@ def domelix_config(z):
     return {"architecture": "Domelix", "vocab": z["vocab"], "width": d, "norm": {"eps": 1e-6}, "layers": layers}
 
 
+def tupunex_config(z):
+    """Three layers of differential attention to one of latent attention, every layer with a gated feed-forward of the
+    Qwen2 decoder's size; four residual streams.  The two maps of a head have half the key size each, so that q, k, v and
+    o have the Qwen2 decoder's shapes; the latent layer caches 512 + 64 numbers per token."""
+    d, H, G, dk = z["width"], z["heads"], z["kv_heads"], z["dim"]
+    inter = -(-(2 * z["ff"] // 3) // 64) * 64
+    mlp = {"kind": "dense", "ff": inter}
+    att = {"type": "attention", "mlp": mlp,
+           "mixer": {"heads": H, "kv_heads": G, "dim": dk // 2, "vdim": dk, "scale": (dk // 2) ** -0.5, "softcap": 30.0, "diff": 0.5, "conv": 4,
+                     "mask": {"size": z["window"]}}}
+    lat = {"type": "latent_attention", "mlp": mlp,
+           "mixer": {"heads": H, "dim": dk, "rot_dim": 64, "vdim": dk, "kv_rank": 512, "scale": (dk + 64) ** -0.5, "rot": {"base": 10000.0, "dims": 64}}}
+    layers = [lat if i % 4 == 2 else att for i in range(z["layers"])]
+    return {"architecture": "Tupunex", "vocab": z["vocab"], "width": d, "norm": {"eps": 1e-6}, "streams": 4, "embedding": {"scale": 1.0},
+            "layers": layers}
+
+
 def qwen2_config(z, context):
     inter = -(-(2 * z["ff"] // 3) // 64) * 64
     return dict(architectures=["Qwen2ForCausalLM"], model_type="qwen2", num_hidden_layers=z["layers"], hidden_size=z["width"],
@@ -211,7 +228,7 @@ def qwen2_config(z, context):
 
 def run_compare(args) -> int:
     """Prefill and decode throughput of one design beside the closest other one at equal size (random weights, bfloat16):
-    Bigerax beside the Qwen2 decoder, Domelix beside Bigerax; one prompt in one step (median of five), and the captured
+    Bigerax beside the Qwen2 decoder, Domelix beside Bigerax, Tupunex beside the Qwen2 decoder; one prompt in one step (median of five), and the captured
     decode step at the given batch over prompts of that length."""
     import numpy as np
     import torch
@@ -227,8 +244,9 @@ def run_compare(args) -> int:
     prompt_len = args.prompt_len or PROMPT_LEN
     steps, warmup, batch = max(1, min(args.steps, 128)), max(3, args.warmup), max(1, args.batch)
     context = -(-(prompt_len + SETTLE_STEPS + warmup + steps + 1) // 1024) * 1024
-    first, second = ("bigerax", "qwen2") if args.compare == "bigerax" else ("domelix", "bigerax")
-    configs = {"bigerax": lambda z: bigerax_config(z), "qwen2": lambda z: qwen2_config(z, context), "domelix": lambda z: domelix_config(z)}
+    first, second = {"bigerax": ("bigerax", "qwen2"), "domelix": ("domelix", "bigerax"), "tupunex": ("tupunex", "qwen2")}[args.compare]
+    configs = {"bigerax": lambda z: bigerax_config(z), "qwen2": lambda z: qwen2_config(z, context), "domelix": lambda z: domelix_config(z),
+               "tupunex": lambda z: tupunex_config(z)}
     out = {"compare": first, "beside": second, "dtype": "bf16", "data": "synthetic", "prompt_len": prompt_len, "batch": batch,
            "steps": steps, "warmup": warmup, "sizes": {}}
     sizes = [args.size] if args.size else sorted(COMPARE_SIZES)
@@ -348,9 +366,9 @@ def main() -> int:
                     help="with --only decode or prefill: prompts of this many tokens instead of 2,048 (the context grows with them)")
     ap.add_argument("--opt", action="append", default=[], metavar="NAME=VALUE",
                     help="set a tunable of the library's dispatch (csrc/exec/exec.h, Options) for this run, e.g. cluster_max_wanted=64")
-    ap.add_argument("--compare", default="", choices=["", "bigerax", "domelix"],
+    ap.add_argument("--compare", default="", choices=["", "bigerax", "domelix", "tupunex"],
                     help="instead of the default run: prefill and decode throughput of that design beside the closest other one (bigerax "
-                         "beside the Qwen2 decoder, domelix beside bigerax) at equal size, at layer sizes that resemble a real model's (random weights; --size, --layers, --batch, --prompt-len, --steps)")
+                         "beside the Qwen2 decoder, domelix beside bigerax, tupunex beside the Qwen2 decoder) at equal size, at layer sizes that resemble a real model's (random weights; --size, --layers, --batch, --prompt-len, --steps)")
     ap.add_argument("--size", default="", choices=[""] + sorted(COMPARE_SIZES), help="with --compare: one size only")
     args = ap.parse_args()
 

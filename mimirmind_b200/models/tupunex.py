@@ -55,6 +55,8 @@ def build_spec(cfg: TupunexConfig) -> ModelSpec:
             extras["ffn_connection"] = connection(2)
         else:
             ffn, ffn_norm = PartSpec("none", {}), PartSpec("none", {})
+            spare = [("norm2", (d,)), ("ls2", (d,))] + ([("hc2.in", (S,)), ("hc2.out", (S,)), ("hc2.mix", (S, S))] if S else [])
+            extras["unused"] = PartSpec("unused_sublayer", {"tensors": spare}, category="connection")
         layers.append(LayerSpec(prefix=f"l{i}.", block=PartSpec("stream_connections", {}), mixer=mixer, feed_forward=ffn,
                                 mixer_norm=norm("norm1"), ffn_norm=ffn_norm, extras=extras))
     return ModelSpec(

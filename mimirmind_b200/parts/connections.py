@@ -77,3 +77,14 @@ class HyperConnection(Part):
         """The sum of the streams, fp32 [n, D] (diagnostics)."""
         ones = torch.ones(self.streams, dtype=torch.float32, device=residual.device)
         return ops.hc_read(residual, self.streams, ones, None, 0.0, torch.float32)
+
+
+@CONNECTIONS.register("unused_sublayer")
+class UnusedSublayer(Part):
+    """The tensors of a sublayer that a layer does not have (a layer without a feed-forward whose checkpoint still carries
+    the norm, scale and stream weights of one): declared so that the checkpoint passes the check at load, allowed to be
+    absent, never read.  spec params: tensors, a list of (name, shape)."""
+
+    @classmethod
+    def tensor_specs(cls, spec: PartSpec, prefix: str) -> List[TensorSpec]:
+        return [TensorSpec(prefix + name, tuple(int(x) for x in shape), role="norm", optional=True) for name, shape in spec["tensors"]]

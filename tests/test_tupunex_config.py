@@ -71,7 +71,16 @@ def test_what_may_be_absent():
 def test_the_declared_tensors_are_the_checkpoints(name):
     from mimirmind_b200.weights.store import expected_tensors
     _, spec = parse(tu.CONFIGS[name])
-    assert {k: tuple(v.shape) for k, v in expected_tensors(spec).items()} == tu.tensor_shapes(tu.CONFIGS[name])
+    declared = expected_tensors(spec)
+    assert {k: tuple(v.shape) for k, v in declared.items() if not v.optional} == tu.tensor_shapes(tu.CONFIGS[name])
+    # a layer without a feed-forward may still carry the second sublayer's norm, scale and stream weights: allowed, never read
+    spare = {k for k, v in declared.items() if v.optional}
+    S = tu.CONFIGS[name].get("streams")
+    want = set()
+    for i, layer in enumerate(tu.CONFIGS[name]["layers"]):
+        if layer["mlp"] is None:
+            want |= {f"l{i}.norm2", f"l{i}.ls2"} | ({f"l{i}.hc2.in", f"l{i}.hc2.out", f"l{i}.hc2.mix"} if S else set())
+    assert spare == want
 
 
 def _edit(path, value=None, delete=False):
