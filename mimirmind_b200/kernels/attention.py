@@ -174,3 +174,75 @@ def paged_sink_attention(q, cache, out, ctx, num_heads: int, num_kv_heads: int, 
     return ops.attention_sink_generic(q, k_pages, v_pages, out, ctx.positions, ctx.token_req, table, cache.page_size, num_heads,
                                       num_kv_heads, key_dim, value_dim, window, scale, sink, sink_logit=sink_logit, dist_bias=dist_bias,
                                       softcap=softcap, value_heads=value_heads, value_row=value_row)
+
+
+USE_LATENT_MMA = True      # False: the latent attention always runs the fp32-arithmetic kernel (tests compare the two)
+LATENT_TILE_ROWS = 32
+LATENT_KEYS = 32
+_latent_declared = False
+
+
+def _latent_lib():
+    global _latent_declared
+    from ctypes import c_float, c_int, c_void_p
+    from . import lib as _lib
+    if not _latent_declared:
+        P, I, F = c_void_p, c_int, c_float
+        _lib.declare("mm_attention_latent_supported", [I, I])
+        _lib.declare("mm_attention_latent_bf16", [P, P, P, P, P, I, P, I, I, P, P, I, I, I, I, I, I, F, I, P])
+        _latent_declared = True
+    return _lib.load()
+
+
+def latent_plan(ctx, num_heads: int):
+    """The step's (token, head) pairs cut once, on the host, into tiles of at most LATENT_TILE_ROWS rows of one request:
+    several tokens with all their heads, or one token with a slice of its heads.  A tile names tokens, not positions
+    (the kernel reads those from the device), so a captured step replays the same plan.  Returns (tiles [n, 5], n)."""
+    key = ("latent_attention_plan", num_heads)
+    plan = ctx.plans.get(key)
+    if plan is None:
+        tiles = []
+        per = max(1, LATENT_TILE_ROWS // num_heads)
+        for r in range(ctx.n_requests):
+            s, n, kv = ctx.q_start[r], ctx.q_len[r], ctx.kv_len[r]
+            for off in range(0, n, per):
+                tokens = min(per, n - off)
+                for h0 in range(0, num_heads, LATENT_TILE_ROWS):
+                    tiles.append((kv - n + off + tokens, r, s + off, tokens, h0, min(LATENT_TILE_ROWS, num_heads - h0)))
+        tiles.sort(key=lambda t: t[0])           # the kernel starts the last (longest) tiles first
+        host = torch.tensor([t[1:] for t in tiles], dtype=torch.int32).reshape(-1, 5).pin_memory()
+        plan = ctx.plans[key] = (host.to(ctx.positions.device, non_blocking=True), len(tiles))
+        ctx.plans[key + ("staged",)] = host
+    return plan
+
+
+def paged_latent_attention(q, pages, cache, out, ctx, num_heads: int, wide: int, rank: int, window: int, scale: float) -> torch.Tensor:
+    """Attention of ``num_heads`` query heads of ``wide`` numbers over one shared key head ``pages`` [pages, 1, page, wide]
+    whose leading ``rank`` numbers are the value; ``out`` [n, num_heads * rank].  bfloat16 with a rank the tensor-core
+    kernel is built for: that kernel, its key tiles shared out over several CTAs while the step has few query tiles;
+    anything else: the fp32-arithmetic kernel."""
+    if USE_LATENT_MMA and q.dtype == torch.bfloat16 and scale > 0 and _latent_lib().mm_attention_latent_supported(wide, rank):
+        from .lib import check
+        lib = _latent_lib()
+        tiles, n_tiles = latent_plan(ctx, num_heads)
+        keys = min(window, ctx.max_kv_len) if window > 0 else ctx.max_kv_len
+        splits = 1
+        if n_tiles < SINK_TARGET_CTAS // 2:
+            splits = max(1, min(-(-SINK_TARGET_CTAS // n_tiles), -(-keys // (4 * LATENT_KEYS)), SINK_MAX_SPLITS))
+        n_rows = q.shape[0] * num_heads
+        part_o = part_ml = None
+        if splits > 1:
+            skey = ("latent_attention_scratch", n_rows, splits, rank)
+            if skey not in ctx.plans:
+                ctx.plans[skey] = (torch.empty((n_rows, splits, rank), dtype=torch.float32, device=q.device),
+                                   torch.empty((n_rows, splits, 2), dtype=torch.float32, device=q.device))
+            part_o, part_ml = ctx.plans[skey]
+        check(lib.mm_attention_latent_bf16(q.data_ptr(), pages.data_ptr(), out.data_ptr(),
+                                           part_o.data_ptr() if part_o is not None else None,
+                                           part_ml.data_ptr() if part_ml is not None else None, splits, tiles.data_ptr(), n_tiles, n_rows,
+                                           ctx.positions.data_ptr(), cache.block_table.data_ptr(), cache.block_table.shape[1],
+                                           cache.page_size, num_heads, wide, rank, int(window), float(scale),
+                                           int(out.dtype == torch.float32), ops._stream()), "attention_latent_bf16")
+        return out
+    return ops.attention_sink_generic(q, pages, pages, out, ctx.positions, ctx.token_req, cache.block_table, cache.page_size, num_heads,
+                                      1, wide, rank, window, scale, False, value_heads=1, value_row=wide)

@@ -106,8 +106,7 @@ class LatentAttention(Mixer):
         ops.head_matmul(q_plain, self.m_key, q_full, H)                      # each head's first `rank` places: Wuk_h^T q_plain
         att = torch.empty((n, H * r), dtype=self.rt.dtype, device=a.device)
         from ..kernels import attention as attn_kernels
-        attn_kernels.paged_sink_attention(q_full, cache, att, ctx, H, 1, wide, r, 0, self.scale, False,
-                                          k_pages=pages, v_pages=pages, value_row=wide)
+        attn_kernels.paged_latent_attention(q_full, pages, cache, att, ctx, H, wide, r, 0, self.scale)
         o = torch.empty((n, H * dv), dtype=self.rt.dtype, device=a.device)
         ops.head_matmul(att, self.m_value, o, H)
         if self.has_gate:

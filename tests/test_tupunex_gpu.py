@@ -206,7 +206,7 @@ def test_two_maps_over_the_same_values(H, G, dk, dv, window, cap, page, dtype):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("style,window,page", [("maps", 40, 16), ("maps", 64, 16), ("maps", 17, 8), ("maps", 65, 32), ("maps", 1, 16),
-                                               ("maps", 0, 16), ("latent", 0, 16), ("latent", 0, 64)])
+                                               ("maps", 0, 16), ("latent", 0, 16), ("latent", 0, 64), ("latent", 33, 16), ("latent", 32, 8)])
 @pytest.mark.parametrize("dk,dv", [(32, 64), (12, 8), (64, 64)])
 def test_one_key_that_stands_out_is_seen_exactly_inside_the_window(style, window, page, dtype, dk, dv):
     """Every key is orthogonal to the query but one, whose score stands out by far and whose value is a marker: the
@@ -246,18 +246,88 @@ def test_one_key_that_stands_out_is_seen_exactly_inside_the_window(style, window
                 q[:, :, dv] = 25.0
                 pool, table = paged(row, page, rng, DT[dtype])
                 cache = LayerCache(arrays={"latent": pool}, block_table=table, page_size=page)
-                kw = dict(k_pages=pool, v_pages=pool, value_row=wide)
                 heads, kv_heads, key_dim, value_dim = H, 1, wide, dv
             for lo in (query, max(0, query - 50), max(0, query - 1)):          # decoded alone; the last of a portion; of two tokens
                 n = query + 1 - lo
                 out = torch.empty((n, heads * value_dim), dtype=DT[dtype], device=DEV)
-                attention.paged_sink_attention(dev(q[lo:query + 1].reshape(n, heads * key_dim), DT[dtype]), cache, out, Ctx(lo, query + 1), heads,
-                                               kv_heads, key_dim, value_dim, window, 1.0, False, **kw)
+                if style == "latent":
+                    attention.paged_latent_attention(dev(q[lo:query + 1].reshape(n, heads * key_dim), DT[dtype]), pool, cache, out,
+                                                     Ctx(lo, query + 1), heads, wide, dv, window, 1.0)
+                else:
+                    attention.paged_sink_attention(dev(q[lo:query + 1].reshape(n, heads * key_dim), DT[dtype]), cache, out, Ctx(lo, query + 1), heads,
+                                                   kv_heads, key_dim, value_dim, window, 1.0, False, **kw)
                 last = out[-1].float().cpu().numpy()
                 if inside:
                     assert (last > 4.8).all(), f"query {query}, key {spot}, window {window}, from {lo}: the key was not seen"
                 elif spot < query:          # the query's own key is always visible, so the weights go to small values
                     assert (np.abs(last) < 0.2).all(), f"query {query}, key {spot}, window {window}, from {lo}: a hidden key was seen"
+
+
+class BatchCtx:
+    """What an attention kernel reads of a step of several requests: request r brings the tokens lo[r]..hi[r]-1."""
+
+    def __init__(self, spans):
+        pos, req, self.q_start, self.q_len, self.kv_len = [], [], [], [], []
+        for r, (lo, hi) in enumerate(spans):
+            self.q_start.append(len(pos))
+            self.q_len.append(hi - lo)
+            self.kv_len.append(hi)
+            pos += list(range(lo, hi))
+            req += [r] * (hi - lo)
+        self.positions = torch.tensor(pos, dtype=torch.int32, device=DEV)
+        self.token_req = torch.tensor(req, dtype=torch.int32, device=DEV)
+        self.n_requests, self.max_q_len, self.max_kv_len = len(spans), max(self.q_len), max(self.kv_len)
+        self.derived, self.plans = {}, {}
+
+
+@pytest.mark.parametrize("target_ctas", [296, 100000])
+@pytest.mark.parametrize("H,rank,extra,page,window", [(4, 64, 32, 16, 0), (3, 96, 32, 16, 0), (40, 32, 8, 8, 0), (16, 512, 64, 64, 0),
+                                                      (1, 48, 16, 32, 0), (5, 128, 24, 16, 45), (2, 256, 64, 16, 0), (33, 16, 8, 16, 100)])
+def test_many_heads_over_one_shared_key_head_whose_leading_part_is_the_value(H, rank, extra, page, window, target_ctas, monkeypatch):
+    """The tensor-core kernel of the latent attention against the sum written out in float64: a step of a long portion,
+    a portion of two tokens, a portion that starts at position 0 and single tokens of several requests, each with pages
+    of its own in one pool; head counts below, at and above a tile's rows; with the key tiles of a row in one CTA and
+    shared out over many."""
+    from mimirmind_b200.kernels import attention
+    from mimirmind_b200.parts.base import LayerCache
+    assert attention._latent_lib().mm_attention_latent_supported(rank + extra, rank)
+    monkeypatch.setattr(attention, "SINK_TARGET_CTAS", target_ctas)
+    rng = np.random.RandomState(H * 1000 + rank)
+    wide = rank + extra
+    spans = [(130, 331), (258, 260), (0, 37), (299, 300), (0, 1), (64, 65), (31, 33)]
+    rows = [bf16_round(rng.randn(hi, 1, wide) * 0.7) for _, hi in spans]
+    width = max(-(-hi // page) for _, hi in spans)
+    n_pages = sum(-(-hi // page) for _, hi in spans) + 3
+    order = rng.permutation(n_pages)
+    pool = torch.full((n_pages, 1, page, wide), float("nan"), dtype=torch.bfloat16, device=DEV)    # an unwritten row must never be read
+    table = np.zeros((len(spans), width), dtype=np.int32)
+    at = 0
+    for r, (_, hi) in enumerate(spans):
+        for p in range(-(-hi // page)):
+            table[r, p] = order[at]
+            n = min(page, hi - p * page)
+            pool[int(order[at]), 0, :n] = dev(rows[r][p * page:p * page + n, 0], torch.bfloat16)
+            at += 1
+    ctx = BatchCtx(spans)
+    n = int(ctx.positions.numel())
+    q = bf16_round(rng.randn(n, H, wide))
+    scale = 0.9 / np.sqrt(wide)
+    want = np.zeros((n, H, rank))
+    for r, (lo, hi) in enumerate(spans):
+        for t in range(lo, hi):
+            first = max(0, t + 1 - window) if window else 0
+            keys = rows[r][first:t + 1, 0]
+            sc = np.einsum("hw,jw->hj", q[ctx.q_start[r] + t - lo], keys) * scale
+            w = np.exp(sc - sc.max(axis=1, keepdims=True))
+            want[ctx.q_start[r] + t - lo] = (w / w.sum(axis=1, keepdims=True)) @ keys[:, :rank]
+    cache = LayerCache(arrays={"latent": pool}, block_table=torch.from_numpy(table).to(DEV), page_size=page)
+    for out_dtype, tol in ((torch.float32, 6e-3), (torch.bfloat16, 1.2e-2)):
+        out = torch.full((n, H * rank), float("nan"), dtype=out_dtype, device=DEV)
+        attention.paged_latent_attention(dev(q.reshape(n, H * wide), torch.bfloat16), pool, cache, out, ctx, H, wide, rank, window, scale)
+        got = out.float().cpu().numpy().reshape(n, H, rank)
+        assert np.isfinite(got).all()
+        err = np.abs(got - want).max(axis=(1, 2)) / np.abs(want).max()
+        assert err.max() < tol, f"token row {int(err.argmax())}: {err.max()}"
 
 
 @pytest.mark.parametrize("taps,C", [(3, 40), (1, 7), (8, 130), (2, 512)])
@@ -311,7 +381,7 @@ def check_rows(trace, outputs, reqs, ref, dtype, what, tol=None):
     for rid, toks in reqs.items():
         rows = np.stack([got[(rid, p)] for p in range(len(toks))])
         err = rel_rms(rows, ref[rid])
-        if dtype == "bfloat16" and err.max() <= 2.5 * tol and (err > tol).mean() <= 0.02:
+        if dtype == "bfloat16" and err.max() <= 2.5 * tol and (err > tol).sum() <= max(2, 0.02 * len(err)):
             # sharp scores and a difference of maps normed to unit size magnify the rounding of single positions (another
             # position with every change of a rounding); the 32-bit run of the same schedule has to be within its bound everywhere
             continue
