@@ -21,7 +21,7 @@
 #include "common.cuh"
 #include "mma_sync.cuh"
 
-#define LAT_ROWS 32        // query rows per CTA
+// query rows per CTA: 32 or 64 (MT 16-row tiles for each of the 2 row groups)
 #define LAT_KEYS 32        // keys per tile
 #define LAT_THREADS 256    // 8 warps: 2 row groups x 4 column groups
 #define LAT_SS 33          // stride of a row of partial scores (floats)
@@ -48,21 +48,24 @@ __device__ __forceinline__ void latent_load_keys(__nv_bfloat16* dst, const __nv_
 }
 
 // tiles: int32 [n_tiles, 5] = (request, first token row, tokens, first head, heads); row r of the tile is token
-// first + r / heads, head first_head + r % heads; tokens * heads <= 32.
-template <int NT>
+// first + r / heads, head first_head + r % heads; tokens * heads <= 32 MT.  MT: 16-row tiles per warp (a CTA owns 32 MT rows).
+template <int NT, int MT>
 __global__ void __launch_bounds__(LAT_THREADS) attention_latent_kernel(
     const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ pool, __nv_bfloat16* __restrict__ out,
     float* __restrict__ out32, float* __restrict__ part_o, float* __restrict__ part_ml, const int32_t* __restrict__ tiles,
     const int32_t* __restrict__ positions, const int32_t* __restrict__ block_table, int table_width, int page_size, int H,
     int wide, int rank, int window, float scale_log2) {
+    constexpr int ROWS = 32 * MT;                 // query rows of the CTA
+    constexpr int TPR = LAT_THREADS / ROWS;       // threads per row in the softmax stage
+    constexpr int KPT = LAT_KEYS / TPR;           // keys per thread there
     const int WP = (wide + 15) & ~15, WS = WP + 8, KSTEPS = WP / 16;
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem_raw);           // [32][WS]
-    __nv_bfloat16* sK = sQ + LAT_ROWS * WS;                                   // [2][32][WS]
-    float* sS = reinterpret_cast<float*>(sK + 2 * LAT_KEYS * WS);             // [4][32][LAT_SS]
-    float* sAlpha = sS + 4 * LAT_ROWS * LAT_SS;                               // [32]
-    int* sPos = reinterpret_cast<int*>(sAlpha + LAT_ROWS);                    // [32]
-    __nv_bfloat16* sP = reinterpret_cast<__nv_bfloat16*>(sPos + LAT_ROWS);    // [32][LAT_PS]
+    __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem_raw);           // [ROWS][WS]
+    __nv_bfloat16* sK = sQ + ROWS * WS;                                       // [2][32][WS]
+    float* sS = reinterpret_cast<float*>(sK + 2 * LAT_KEYS * WS);             // [4][ROWS][LAT_SS]
+    float* sAlpha = sS + 4 * ROWS * LAT_SS;                                   // [ROWS]
+    int* sPos = reinterpret_cast<int*>(sAlpha + ROWS);                        // [ROWS]
+    __nv_bfloat16* sP = reinterpret_cast<__nv_bfloat16*>(sPos + ROWS);        // [ROWS][LAT_PS]
 
     const int tile = gridDim.x - 1 - blockIdx.x, split = blockIdx.y, n_splits = gridDim.y;
     const int req = tiles[tile * 5 + 0], tok0 = tiles[tile * 5 + 1], n_tok = tiles[tile * 5 + 2];
@@ -71,6 +74,7 @@ __global__ void __launch_bounds__(LAT_THREADS) attention_latent_kernel(
     const int32_t* table = block_table + (size_t)req * table_width;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int rg = warp >> 2, cg = warp & 3;
+    const int row_base = rg * 16 * MT;            // this warp's first row
 
     const int pos_first = positions[tok0], pos_last = positions[tok0 + n_tok - 1];
     const int hi_all = pos_last + 1;
@@ -82,10 +86,10 @@ __global__ void __launch_bounds__(LAT_THREADS) attention_latent_kernel(
         kt_end = min(kt_end, kt_begin + per);
     }
 
-    if (threadIdx.x < LAT_ROWS) sPos[threadIdx.x] = threadIdx.x < n_rows ? positions[tok0 + threadIdx.x / n_heads] : -1;
+    if (threadIdx.x < ROWS) sPos[threadIdx.x] = threadIdx.x < n_rows ? positions[tok0 + threadIdx.x / n_heads] : -1;
     {
         const int chunks = WP / 8, real = wide / 8;
-        for (int c = threadIdx.x; c < LAT_ROWS * chunks; c += LAT_THREADS) {
+        for (int c = threadIdx.x; c < ROWS * chunks; c += LAT_THREADS) {
             const int r = c / chunks, part = c - r * chunks;
             uint4 v = make_uint4(0, 0, 0, 0);
             if (r < n_rows && part < real) {
@@ -100,11 +104,13 @@ __global__ void __launch_bounds__(LAT_THREADS) attention_latent_kernel(
         latent_load_keys(sK, pool, table, kt_begin * LAT_KEYS, lo_all, hi_all, page_size, page_shift, wide, WS);
     cp_async_commit();
 
-    float o[NT][4];
+    float o[MT][NT][4];
 #pragma unroll
-    for (int j = 0; j < NT; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.0f;
-    // the softmax stage: thread t holds row t / 8 and the keys (t % 8) * 4 .. + 3 of a tile
-    const int srow = threadIdx.x >> 3, skey = (threadIdx.x & 7) * 4;
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+        for (int j = 0; j < NT; ++j) o[mt][j][0] = o[mt][j][1] = o[mt][j][2] = o[mt][j][3] = 0.0f;
+    // the softmax stage: thread t holds row t / TPR and the keys (t % TPR) * KPT .. + KPT - 1 of a tile
+    const int srow = threadIdx.x / TPR, skey = (threadIdx.x % TPR) * KPT;
     float m_run = -INFINITY, l_run = 0.0f;
     const int col0 = cg * NT * 8;                    // this warp's first value column
     const int id = lane >> 3, rr = lane & 7;
@@ -120,29 +126,40 @@ __global__ void __launch_bounds__(LAT_THREADS) attention_latent_kernel(
         }
         const __nv_bfloat16* tK = sK + buf * LAT_KEYS * WS;
         const int key0 = kt * LAT_KEYS;
-        // 1. partial scores of 16 rows x 32 keys over this warp's slices
+        // 1. partial scores of 16 MT rows x 32 keys over this warp's slices
         {
-            float s[4][4];
+            float s[MT][4][4];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.0f;
+            for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) s[mt][j][0] = s[mt][j][1] = s[mt][j][2] = s[mt][j][3] = 0.0f;
             for (int ks = cg; ks < KSTEPS; ks += 4) {
-                uint32_t a[4];
-                ldmatrix_x4(a[0], a[1], a[2], a[3], sQ + (rg * 16 + (id & 1) * 8 + rr) * WS + ks * 16 + (id >> 1) * 8);
+                uint32_t a[MT][4];
+#pragma unroll
+                for (int mt = 0; mt < MT; ++mt)
+                    ldmatrix_x4(a[mt][0], a[mt][1], a[mt][2], a[mt][3],
+                                sQ + (row_base + mt * 16 + (id & 1) * 8 + rr) * WS + ks * 16 + (id >> 1) * 8);
 #pragma unroll
                 for (int jp = 0; jp < 2; ++jp) {
                     uint32_t b0, b1, b2, b3;
                     ldmatrix_x4(b0, b1, b2, b3, tK + (jp * 16 + (id >> 1) * 8 + rr) * WS + ks * 16 + (id & 1) * 8);
-                    mma_bf16(s[jp * 2], a, b0, b1);
-                    mma_bf16(s[jp * 2 + 1], a, b2, b3);
+#pragma unroll
+                    for (int mt = 0; mt < MT; ++mt) {
+                        mma_bf16(s[mt][jp * 2], a[mt], b0, b1);
+                        mma_bf16(s[mt][jp * 2 + 1], a[mt], b2, b3);
+                    }
                 }
             }
-            float* dst = sS + (cg * LAT_ROWS + rg * 16 + (lane >> 2)) * LAT_SS + (lane & 3) * 2;
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                dst[j * 8] = s[j][0];
-                dst[j * 8 + 1] = s[j][1];
-                dst[8 * LAT_SS + j * 8] = s[j][2];
-                dst[8 * LAT_SS + j * 8 + 1] = s[j][3];
+            for (int mt = 0; mt < MT; ++mt) {
+                float* dst = sS + (cg * ROWS + row_base + mt * 16 + (lane >> 2)) * LAT_SS + (lane & 3) * 2;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    dst[j * 8] = s[mt][j][0];
+                    dst[j * 8 + 1] = s[mt][j][1];
+                    dst[8 * LAT_SS + j * 8] = s[mt][j][2];
+                    dst[8 * LAT_SS + j * 8 + 1] = s[mt][j][3];
+                }
             }
         }
         __syncthreads();
@@ -150,55 +167,63 @@ __global__ void __launch_bounds__(LAT_THREADS) attention_latent_kernel(
         {
             const int pos = sPos[srow];
             const int wlo = (window > 0 && pos + 1 > window) ? pos + 1 - window : 0;
-            float sc[4];
+            float sc[KPT];
             float mx = m_run;
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
+            for (int e = 0; e < KPT; ++e) {
                 const float* src = sS + srow * LAT_SS + skey + e;
-                const float v = (src[0] + src[LAT_ROWS * LAT_SS]) + (src[2 * LAT_ROWS * LAT_SS] + src[3 * LAT_ROWS * LAT_SS]);
+                const float v = (src[0] + src[ROWS * LAT_SS]) + (src[2 * ROWS * LAT_SS] + src[3 * ROWS * LAT_SS]);
                 const int key = key0 + skey + e;
                 sc[e] = (key <= pos && key >= wlo) ? v * scale_log2 : -INFINITY;
                 mx = fmaxf(mx, sc[e]);
             }
-            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+#pragma unroll
+            for (int d = 1; d < TPR; d <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, d));
             const float use = mx == -INFINITY ? 0.0f : mx;
             const float alpha = exp2f(m_run - use);        // m_run = -inf: 0
-            float p[4], sum = 0.0f;
+            float sum = 0.0f;
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                p[e] = exp2f(sc[e] - use);
-                sum += p[e];
+            for (int e = 0; e < KPT; ++e) {
+                sc[e] = exp2f(sc[e] - use);
+                sum += sc[e];
             }
-            sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-            sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-            sum += __shfl_xor_sync(0xffffffffu, sum, 4);
+#pragma unroll
+            for (int d = 1; d < TPR; d <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, d);
             l_run = l_run * alpha + sum;
             m_run = mx;
-            uint2 packed = make_uint2(pack_bf16(p[0], p[1]), pack_bf16(p[2], p[3]));
-            *reinterpret_cast<uint2*>(sP + srow * LAT_PS + skey) = packed;
-            if ((threadIdx.x & 7) == 0) sAlpha[srow] = alpha;
+#pragma unroll
+            for (int e = 0; e < KPT; e += 4)
+                *reinterpret_cast<uint2*>(sP + srow * LAT_PS + skey + e) = make_uint2(pack_bf16(sc[e], sc[e + 1]), pack_bf16(sc[e + 2], sc[e + 3]));
+            if (threadIdx.x % TPR == 0) sAlpha[srow] = alpha;
         }
         __syncthreads();
         // 3. the weights times the leading `rank` numbers of the same rows
         {
-            const float a_lo = sAlpha[rg * 16 + (lane >> 2)], a_hi = sAlpha[rg * 16 + 8 + (lane >> 2)];
 #pragma unroll
-            for (int j = 0; j < NT; ++j) {
-                o[j][0] *= a_lo; o[j][1] *= a_lo; o[j][2] *= a_hi; o[j][3] *= a_hi;
+            for (int mt = 0; mt < MT; ++mt) {
+                const float a_lo = sAlpha[row_base + mt * 16 + (lane >> 2)], a_hi = sAlpha[row_base + mt * 16 + 8 + (lane >> 2)];
+#pragma unroll
+                for (int j = 0; j < NT; ++j) {
+                    o[mt][j][0] *= a_lo; o[mt][j][1] *= a_lo; o[mt][j][2] *= a_hi; o[mt][j][3] *= a_hi;
+                }
             }
 #pragma unroll
             for (int ks = 0; ks < 2; ++ks) {
-                uint32_t a[4];
-                ldmatrix_x4(a[0], a[1], a[2], a[3], sP + (rg * 16 + (id & 1) * 8 + rr) * LAT_PS + ks * 16 + (id >> 1) * 8);
+                uint32_t a[MT][4];
+#pragma unroll
+                for (int mt = 0; mt < MT; ++mt)
+                    ldmatrix_x4(a[mt][0], a[mt][1], a[mt][2], a[mt][3],
+                                sP + (row_base + mt * 16 + (id & 1) * 8 + rr) * LAT_PS + ks * 16 + (id >> 1) * 8);
 #pragma unroll
                 for (int jp = 0; jp < NT / 2; ++jp) {
                     if (col0 + jp * 16 < rank) {
                         uint32_t b0, b1, b2, b3;
                         ldmatrix_x4_trans(b0, b1, b2, b3, tK + (ks * 16 + (id & 1) * 8 + rr) * WS + col0 + (jp * 2 + (id >> 1)) * 8);
-                        mma_bf16(o[jp * 2], a, b0, b1);
-                        mma_bf16(o[jp * 2 + 1], a, b2, b3);
+#pragma unroll
+                        for (int mt = 0; mt < MT; ++mt) {
+                            mma_bf16(o[mt][jp * 2], a[mt], b0, b1);
+                            mma_bf16(o[mt][jp * 2 + 1], a[mt], b2, b3);
+                        }
                     }
                 }
             }
@@ -206,39 +231,41 @@ __global__ void __launch_bounds__(LAT_THREADS) attention_latent_kernel(
     }
     // every row's mass and maximum, for the warps that hold its accumulators
     __syncthreads();
-    if ((threadIdx.x & 7) == 0) {
+    if (threadIdx.x % TPR == 0) {
         sAlpha[srow] = l_run;
         sS[srow] = m_run;
     }
     __syncthreads();
-    const int r_lo = rg * 16 + (lane >> 2), r_hi = r_lo + 8;
 #pragma unroll
-    for (int half = 0; half < 2; ++half) {
-        const int r = half ? r_hi : r_lo;
-        if (r >= n_rows) continue;
-        const int tok = tok0 + r / n_heads, h = head0 + r % n_heads;
-        const size_t row = (size_t)tok * H + h;
-        const float l = sAlpha[r];
-        if (n_splits > 1) {
-            float* dst = part_o + (row * n_splits + split) * rank;
+    for (int mt = 0; mt < MT; ++mt) {
 #pragma unroll
-            for (int j = 0; j < NT; ++j) {
-                const int col = col0 + j * 8 + (lane & 3) * 2;
-                if (col < rank) *reinterpret_cast<float2*>(dst + col) = make_float2(o[j][half * 2], o[j][half * 2 + 1]);
-            }
-            if (cg == 0 && (lane & 3) == 0) {
-                part_ml[(row * n_splits + split) * 2] = sS[r];
-                part_ml[(row * n_splits + split) * 2 + 1] = l;
-            }
-        } else {
-            const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+        for (int half = 0; half < 2; ++half) {
+            const int r = row_base + mt * 16 + half * 8 + (lane >> 2);
+            if (r >= n_rows) continue;
+            const int tok = tok0 + r / n_heads, h = head0 + r % n_heads;
+            const size_t row = (size_t)tok * H + h;
+            const float l = sAlpha[r];
+            if (n_splits > 1) {
+                float* dst = part_o + (row * n_splits + split) * rank;
 #pragma unroll
-            for (int j = 0; j < NT; ++j) {
-                const int col = col0 + j * 8 + (lane & 3) * 2;
-                if (col >= rank) continue;
-                const float x = o[j][half * 2] * inv, y = o[j][half * 2 + 1] * inv;
-                if (out32 != nullptr) *reinterpret_cast<float2*>(out32 + row * rank + col) = make_float2(x, y);
-                else *reinterpret_cast<uint32_t*>(out + row * rank + col) = pack_bf16(x, y);
+                for (int j = 0; j < NT; ++j) {
+                    const int col = col0 + j * 8 + (lane & 3) * 2;
+                    if (col < rank) *reinterpret_cast<float2*>(dst + col) = make_float2(o[mt][j][half * 2], o[mt][j][half * 2 + 1]);
+                }
+                if (cg == 0 && (lane & 3) == 0) {
+                    part_ml[(row * n_splits + split) * 2] = sS[r];
+                    part_ml[(row * n_splits + split) * 2 + 1] = l;
+                }
+            } else {
+                const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+#pragma unroll
+                for (int j = 0; j < NT; ++j) {
+                    const int col = col0 + j * 8 + (lane & 3) * 2;
+                    if (col >= rank) continue;
+                    const float x = o[mt][j][half * 2] * inv, y = o[mt][j][half * 2 + 1] * inv;
+                    if (out32 != nullptr) *reinterpret_cast<float2*>(out32 + row * rank + col) = make_float2(x, y);
+                    else *reinterpret_cast<uint32_t*>(out + row * rank + col) = pack_bf16(x, y);
+                }
             }
         }
     }
@@ -265,17 +292,22 @@ __global__ void attention_latent_merge_kernel(__nv_bfloat16* __restrict__ out, f
     }
 }
 
-static size_t latent_smem(int wide) {
+
+static size_t latent_smem(int wide, int rows) {
     const int WS = ((wide + 15) & ~15) + 8;
-    return (size_t)3 * LAT_ROWS * WS * 2 + (size_t)4 * LAT_ROWS * LAT_SS * 4 + LAT_ROWS * 8 + (size_t)LAT_ROWS * LAT_PS * 2;
+    return (size_t)(rows + 2 * LAT_KEYS) * WS * 2 + (size_t)4 * rows * LAT_SS * 4 + rows * 8 + (size_t)rows * LAT_PS * 2;
 }
 
-template <int NT>
-static int launch_latent(const void* q, const void* pool, void* out, void* part_o, void* part_ml, int n_splits, const void* tiles,
-                         int n_tiles, int n_rows, const void* positions, const void* table, int table_width, int page_size, int H,
-                         int wide, int rank, int window, float scale, int out_f32, cudaStream_t s) {
-    const size_t smem = latent_smem(wide);
-    auto kernel = attention_latent_kernel<NT>;
+#define LAT_ARGS const void* q, const void* pool, void* out, void* part_o, void* part_ml, int n_splits, const void* tiles, \
+                 int n_tiles, int n_rows, const void* positions, const void* table, int table_width, int page_size, int H, \
+                 int wide, int rank, int window, float scale, int out_f32, cudaStream_t s
+#define LAT_PASS q, pool, out, part_o, part_ml, n_splits, tiles, n_tiles, n_rows, positions, table, table_width, page_size, H, \
+                 wide, rank, window, scale, out_f32, s
+
+template <int NT, int MT>
+static int launch_latent(LAT_ARGS) {
+    const size_t smem = latent_smem(wide, 32 * MT);
+    auto kernel = attention_latent_kernel<NT, MT>;
     static size_t allowed = 0;                     // per instantiation
     if (smem > allowed) {
         if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
@@ -298,26 +330,39 @@ static int launch_latent(const void* q, const void* pool, void* out, void* part_
     return MM_OK;
 }
 
+#define LAT_SMEM_MAX (220 * 1024)
+
 // sizes the kernel takes: rank a multiple of 16 up to 512, wide = rank + extra a multiple of 8 whose tiles fit
 MM_EXPORT int mm_attention_latent_supported(int wide, int rank) {
-    return rank >= 16 && rank <= 512 && rank % 16 == 0 && wide >= rank && wide % 8 == 0 && latent_smem(wide) <= 200 * 1024;
+    return rank >= 16 && rank <= 512 && rank % 16 == 0 && wide >= rank && wide % 8 == 0 && latent_smem(wide, 32) <= LAT_SMEM_MAX;
 }
 
-// q [n, H, wide] and pool [pages, page, wide] bfloat16; out [n, H, rank] bfloat16 or fp32.  tiles int32 [n_tiles, 5];
-// n_rows = n * H.  n_splits > 1: part_o [n_rows, n_splits, rank] and part_ml [n_rows, n_splits, 2] (fp32).
+// the rows of a tile the kernel may be given for this width: 64 where two 16-row tiles per warp fit, else 32
+MM_EXPORT int mm_attention_latent_tile_rows(int wide) { return latent_smem(wide, 64) <= LAT_SMEM_MAX ? 64 : 32; }
+
+// q [n, H, wide] and pool [pages, page, wide] bfloat16; out [n, H, rank] bfloat16 or fp32.  tiles int32 [n_tiles, 5] of at
+// most tile_rows (32 or 64) rows each; n_rows = n * H.  n_splits > 1: part_o [n_rows, n_splits, rank] and part_ml
+// [n_rows, n_splits, 2] (fp32).
 MM_EXPORT int mm_attention_latent_bf16(const void* q, const void* pool, void* out, void* part_o, void* part_ml, int n_splits,
-                                       const void* tiles, int n_tiles, int n_rows, const void* positions, const void* block_table,
-                                       int table_width, int page_size, int H, int wide, int rank, int window, float scale, int out_f32,
-                                       void* stream) {
+                                       const void* tiles, int n_tiles, int tile_rows, int n_rows, const void* positions,
+                                       const void* table, int table_width, int page_size, int H, int wide, int rank, int window,
+                                       float scale, int out_f32, void* stream) {
     MM_REQUIRE(mm_attention_latent_supported(wide, rank), "latent attention: rank a multiple of 16 up to 512, row width a multiple of 8");
+    MM_REQUIRE(tile_rows == 32 || (tile_rows == 64 && mm_attention_latent_tile_rows(wide) == 64), "latent attention: tiles of 32 or 64 rows");
     MM_REQUIRE(n_splits >= 1 && n_splits <= 64 && (n_splits == 1 || (part_o != nullptr && part_ml != nullptr)),
                "latent attention: 1..64 splits, with scratch for more than one");
     MM_REQUIRE(n_tiles >= 0 && H > 0 && page_size > 0 && table_width > 0 && window >= 0 && scale > 0.0f,
                "latent attention: bad heads, page geometry, window or scale");
     if (n_tiles == 0) return MM_OK;
     cudaStream_t s = (cudaStream_t)stream;
-    if (rank <= 64) return launch_latent<2>(q, pool, out, part_o, part_ml, n_splits, tiles, n_tiles, n_rows, positions, block_table, table_width, page_size, H, wide, rank, window, scale, out_f32, s);
-    if (rank <= 128) return launch_latent<4>(q, pool, out, part_o, part_ml, n_splits, tiles, n_tiles, n_rows, positions, block_table, table_width, page_size, H, wide, rank, window, scale, out_f32, s);
-    if (rank <= 256) return launch_latent<8>(q, pool, out, part_o, part_ml, n_splits, tiles, n_tiles, n_rows, positions, block_table, table_width, page_size, H, wide, rank, window, scale, out_f32, s);
-    return launch_latent<16>(q, pool, out, part_o, part_ml, n_splits, tiles, n_tiles, n_rows, positions, block_table, table_width, page_size, H, wide, rank, window, scale, out_f32, s);
+    if (tile_rows == 64) {
+        if (rank <= 64) return launch_latent<2, 2>(LAT_PASS);
+        if (rank <= 128) return launch_latent<4, 2>(LAT_PASS);
+        if (rank <= 256) return launch_latent<8, 2>(LAT_PASS);
+        return launch_latent<16, 2>(LAT_PASS);
+    }
+    if (rank <= 64) return launch_latent<2, 1>(LAT_PASS);
+    if (rank <= 128) return launch_latent<4, 1>(LAT_PASS);
+    if (rank <= 256) return launch_latent<8, 1>(LAT_PASS);
+    return launch_latent<16, 1>(LAT_PASS);
 }

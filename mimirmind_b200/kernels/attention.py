@@ -178,6 +178,7 @@ def paged_sink_attention(q, cache, out, ctx, num_heads: int, num_kv_heads: int, 
 
 USE_LATENT_MMA = True      # False: the latent attention always runs the fp32-arithmetic kernel (tests compare the two)
 LATENT_TILE_ROWS = 32
+USE_LATENT_WIDE_TILES = True    # False: tiles of 32 rows also for portions of prompts (tests run both)
 LATENT_KEYS = 32
 _latent_declared = False
 
@@ -189,26 +190,27 @@ def _latent_lib():
     if not _latent_declared:
         P, I, F = c_void_p, c_int, c_float
         _lib.declare("mm_attention_latent_supported", [I, I])
-        _lib.declare("mm_attention_latent_bf16", [P, P, P, P, P, I, P, I, I, P, P, I, I, I, I, I, I, F, I, P])
+        _lib.declare("mm_attention_latent_tile_rows", [I])
+        _lib.declare("mm_attention_latent_bf16", [P, P, P, P, P, I, P, I, I, I, P, P, I, I, I, I, I, I, F, I, P])
         _latent_declared = True
     return _lib.load()
 
 
-def latent_plan(ctx, num_heads: int):
-    """The step's (token, head) pairs cut once, on the host, into tiles of at most LATENT_TILE_ROWS rows of one request:
+def latent_plan(ctx, num_heads: int, tile_rows: int = LATENT_TILE_ROWS):
+    """The step's (token, head) pairs cut once, on the host, into tiles of at most ``tile_rows`` rows of one request:
     several tokens with all their heads, or one token with a slice of its heads.  A tile names tokens, not positions
     (the kernel reads those from the device), so a captured step replays the same plan.  Returns (tiles [n, 5], n)."""
-    key = ("latent_attention_plan", num_heads)
+    key = ("latent_attention_plan", num_heads, tile_rows)
     plan = ctx.plans.get(key)
     if plan is None:
         tiles = []
-        per = max(1, LATENT_TILE_ROWS // num_heads)
+        per = max(1, tile_rows // num_heads)
         for r in range(ctx.n_requests):
             s, n, kv = ctx.q_start[r], ctx.q_len[r], ctx.kv_len[r]
             for off in range(0, n, per):
                 tokens = min(per, n - off)
-                for h0 in range(0, num_heads, LATENT_TILE_ROWS):
-                    tiles.append((kv - n + off + tokens, r, s + off, tokens, h0, min(LATENT_TILE_ROWS, num_heads - h0)))
+                for h0 in range(0, num_heads, tile_rows):
+                    tiles.append((kv - n + off + tokens, r, s + off, tokens, h0, min(tile_rows, num_heads - h0)))
         tiles.sort(key=lambda t: t[0])           # the kernel starts the last (longest) tiles first
         host = torch.tensor([t[1:] for t in tiles], dtype=torch.int32).reshape(-1, 5).pin_memory()
         plan = ctx.plans[key] = (host.to(ctx.positions.device, non_blocking=True), len(tiles))
@@ -224,7 +226,9 @@ def paged_latent_attention(q, pages, cache, out, ctx, num_heads: int, wide: int,
     if USE_LATENT_MMA and q.dtype == torch.bfloat16 and scale > 0 and _latent_lib().mm_attention_latent_supported(wide, rank):
         from .lib import check
         lib = _latent_lib()
-        tiles, n_tiles = latent_plan(ctx, num_heads)
+        # portions of prompts: tiles of 64 rows (two 16-row tiles per warp, half the key traffic per row) where they fit
+        tile_rows = 64 if USE_LATENT_WIDE_TILES and ctx.max_q_len * num_heads >= 64 and lib.mm_attention_latent_tile_rows(wide) == 64 else LATENT_TILE_ROWS
+        tiles, n_tiles = latent_plan(ctx, num_heads, tile_rows)
         keys = min(window, ctx.max_kv_len) if window > 0 else ctx.max_kv_len
         splits = 1
         if n_tiles < SINK_TARGET_CTAS // 2:
@@ -239,7 +243,7 @@ def paged_latent_attention(q, pages, cache, out, ctx, num_heads: int, wide: int,
             part_o, part_ml = ctx.plans[skey]
         check(lib.mm_attention_latent_bf16(q.data_ptr(), pages.data_ptr(), out.data_ptr(),
                                            part_o.data_ptr() if part_o is not None else None,
-                                           part_ml.data_ptr() if part_ml is not None else None, splits, tiles.data_ptr(), n_tiles, n_rows,
+                                           part_ml.data_ptr() if part_ml is not None else None, splits, tiles.data_ptr(), n_tiles, tile_rows, n_rows,
                                            ctx.positions.data_ptr(), cache.block_table.data_ptr(), cache.block_table.shape[1],
                                            cache.page_size, num_heads, wide, rank, int(window), float(scale),
                                            int(out.dtype == torch.float32), ops._stream()), "attention_latent_bf16")

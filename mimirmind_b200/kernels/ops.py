@@ -1324,6 +1324,9 @@ def latent_prep(rows: torch.Tensor, q_off: int, c_off: int, norm_weight: torch.T
                                      int(rot_dim), int(rank), _stream()), "latent_prep")
 
 
+HEAD_MATMUL_LIBRARY_FROM = 64      # rows from which the per-head products of bfloat16 rows are one batched library product
+
+
 def head_matmul(x: torch.Tensor, matrices: torch.Tensor, out: torch.Tensor, heads: int) -> torch.Tensor:
     """``out[t, h, :] = x[t, h, :] . matrices[h]`` with ``matrices`` [heads, K, N]; ``x`` is [n, heads * K] and ``out``
     [n, heads * N'] with N' >= N (each head's result goes to the first N places of its N' wide part); both may be column
@@ -1334,6 +1337,11 @@ def head_matmul(x: torch.Tensor, matrices: torch.Tensor, out: torch.Tensor, head
         raise KernelError("head product: shape mismatch")
     if x.dtype != matrices.dtype or out.dtype != x.dtype or not matrices.is_contiguous() or x.stride(1) != 1 or out.stride(1) != 1:
         raise KernelError("head product: one dtype and unit column strides are needed")
+    if x.dtype == torch.bfloat16 and n >= HEAD_MATMUL_LIBRARY_FROM:
+        # a portion of a prompt: one batched product of the vendor library over the heads, operands and result in place
+        wide = out.shape[1] // H
+        torch.bmm(x.view(n, H, K).transpose(0, 1), matrices, out=out.view(n, H, wide)[:, :, :N].transpose(0, 1))
+        return out
     check(_lib.load().mm_head_matmul(x.data_ptr(), x.stride(0), K, matrices.data_ptr(), out.data_ptr(), out.stride(0), out.shape[1] // H,
                                      dtype_code(x.dtype), n, H, K, N, _stream()), "head_matmul")
     return out

@@ -280,18 +280,19 @@ class BatchCtx:
         self.derived, self.plans = {}, {}
 
 
-@pytest.mark.parametrize("target_ctas", [296, 100000])
+@pytest.mark.parametrize("target_ctas,wide_tiles", [(296, True), (100000, True), (296, False), (100000, False)])
 @pytest.mark.parametrize("H,rank,extra,page,window", [(4, 64, 32, 16, 0), (3, 96, 32, 16, 0), (40, 32, 8, 8, 0), (16, 512, 64, 64, 0),
                                                       (1, 48, 16, 32, 0), (5, 128, 24, 16, 45), (2, 256, 64, 16, 0), (33, 16, 8, 16, 100)])
-def test_many_heads_over_one_shared_key_head_whose_leading_part_is_the_value(H, rank, extra, page, window, target_ctas, monkeypatch):
+def test_many_heads_over_one_shared_key_head_whose_leading_part_is_the_value(H, rank, extra, page, window, target_ctas, wide_tiles, monkeypatch):
     """The tensor-core kernel of the latent attention against the sum written out in float64: a step of a long portion,
     a portion of two tokens, a portion that starts at position 0 and single tokens of several requests, each with pages
     of its own in one pool; head counts below, at and above a tile's rows; with the key tiles of a row in one CTA and
-    shared out over many."""
+    shared out over many; with tiles of 64 rows and of 32."""
     from mimirmind_b200.kernels import attention
     from mimirmind_b200.parts.base import LayerCache
     assert attention._latent_lib().mm_attention_latent_supported(rank + extra, rank)
     monkeypatch.setattr(attention, "SINK_TARGET_CTAS", target_ctas)
+    monkeypatch.setattr(attention, "USE_LATENT_WIDE_TILES", wide_tiles)
     rng = np.random.RandomState(H * 1000 + rank)
     wide = rank + extra
     spans = [(130, 331), (258, 260), (0, 37), (299, 300), (0, 1), (64, 65), (31, 33)]
