@@ -9,7 +9,7 @@
 //     the shared rotated key part and every head's rotated query part are turned (pairs i, i + dims/2), and latent and
 //     rotated key are written side by side into one per-token cache array;
 //   * head_matmul: out[t, h, :] = in[t, h, :] . M[h] with a matrix per head (absorbing the key or value up-projection
-//     of a latent attention into the query or the output), fp32 FMAs in ascending k;
+//     of a latent attention into the query or the output), fp32 FMAs over eight runs of k, summed in order;
 //   * head_finish: what happens to each head's attention output before the output projection: the difference of two
 //     maps (a1 - lambda a2), a division by the head's root mean square, a constant factor, a sigmoid gate per (token, head).
 #include "common.cuh"
@@ -165,30 +165,47 @@ MM_EXPORT int mm_latent_prep(const void* rows, int ld, int q_off, int c_off, con
 // out[t, h, j] = sum_k in[t, h, k] M[h, k, j]; in: token stride in_ld, head stride in_hs; out likewise.  Eight tokens
 // of one head per block share each matrix element; a thread owns one output column.
 #define HM_TOKENS 8
+#define HM_COLS 64
+#define HM_SLICES 8
+// A block of HM_COLS x HM_SLICES threads makes HM_TOKENS tokens x HM_COLS columns of one head: slice y sums its run of k
+// (ascending), then thread (x, y) adds the slices' sums of token y in slice order.  The cut of k depends on K alone, so
+// a token's result never depends on the batch.
 template <typename T>
-__global__ void head_matmul_kernel(const T* __restrict__ in, long long in_ld, int in_hs, const T* __restrict__ M, T* __restrict__ out,
-                                   long long out_ld, int out_hs, int n_tokens, int K, int N) {
+__global__ void __launch_bounds__(HM_COLS * HM_SLICES) head_matmul_kernel(
+    const T* __restrict__ in, long long in_ld, int in_hs, const T* __restrict__ M, T* __restrict__ out, long long out_ld, int out_hs,
+    int n_tokens, int K, int N) {
     extern __shared__ float in_s[];   // [HM_TOKENS][K]
+    __shared__ float part[HM_SLICES][HM_TOKENS][HM_COLS];
     const int h = blockIdx.y, t0 = blockIdx.z * HM_TOKENS;
-    const int j = blockIdx.x * blockDim.x + threadIdx.x;
-    for (int i = threadIdx.x; i < HM_TOKENS * K; i += blockDim.x) {
+    const int x = threadIdx.x, y = threadIdx.y, tid = y * HM_COLS + x;
+    const int j = blockIdx.x * HM_COLS + x;
+    for (int i = tid; i < HM_TOKENS * K; i += HM_COLS * HM_SLICES) {
         const int tt = i / K, k = i - tt * K;
         in_s[i] = (t0 + tt < n_tokens) ? to_f32<T>(in[(size_t)(t0 + tt) * in_ld + (size_t)h * in_hs + k]) : 0.0f;
     }
     __syncthreads();
-    if (j >= N) return;
     float acc[HM_TOKENS];
 #pragma unroll
     for (int tt = 0; tt < HM_TOKENS; ++tt) acc[tt] = 0.0f;
-    const T* Mh = M + (size_t)h * K * N + j;
-    for (int k = 0; k < K; ++k) {
-        const float w = to_f32<T>(Mh[(size_t)k * N]);
+    const int per = (K + HM_SLICES - 1) / HM_SLICES;
+    const int k_lo = y * per, k_hi = min(K, k_lo + per);
+    if (j < N) {
+        const T* Mh = M + (size_t)h * K * N + j;
+#pragma unroll 4
+        for (int k = k_lo; k < k_hi; ++k) {
+            const float w = to_f32<T>(Mh[(size_t)k * N]);
 #pragma unroll
-        for (int tt = 0; tt < HM_TOKENS; ++tt) acc[tt] = fmaf(in_s[tt * K + k], w, acc[tt]);
+            for (int tt = 0; tt < HM_TOKENS; ++tt) acc[tt] = fmaf(in_s[tt * K + k], w, acc[tt]);
+        }
     }
 #pragma unroll
-    for (int tt = 0; tt < HM_TOKENS; ++tt)
-        if (t0 + tt < n_tokens) out[(size_t)(t0 + tt) * out_ld + (size_t)h * out_hs + j] = from_f32<T>(acc[tt]);
+    for (int tt = 0; tt < HM_TOKENS; ++tt) part[y][tt][x] = acc[tt];
+    __syncthreads();
+    if (j >= N || t0 + y >= n_tokens) return;
+    float sum = 0.0f;
+#pragma unroll
+    for (int sl = 0; sl < HM_SLICES; ++sl) sum += part[sl][y][x];
+    out[(size_t)(t0 + y) * out_ld + (size_t)h * out_hs + j] = from_f32<T>(sum);
 }
 
 MM_EXPORT int mm_head_matmul(const void* in, long long in_ld, int in_hs, const void* M, void* out, long long out_ld, int out_hs, int dtype,
@@ -198,18 +215,18 @@ MM_EXPORT int mm_head_matmul(const void* in, long long in_ld, int in_hs, const v
     if (n_tokens == 0) return MM_OK;
     cudaStream_t s = (cudaStream_t)stream;
     const size_t smem = (size_t)HM_TOKENS * K * sizeof(float);
-    const dim3 grid(ceil_div(N, 128), H, ceil_div(n_tokens, HM_TOKENS));
+    const dim3 grid(ceil_div(N, HM_COLS), H, ceil_div(n_tokens, HM_TOKENS)), block(HM_COLS, HM_SLICES);
     if (grid.z > 65535) {
         mm_set_last_error("head product: too many tokens for one launch");
         return MM_ERR_BAD_ARG;
     }
     if (dtype == MM_F32) {
-        if (smem > 48 * 1024) cudaFuncSetAttribute(head_matmul_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        mm_launch(head_matmul_kernel<float>, grid, dim3(128), smem, s, (const float*)in, in_ld, in_hs, (const float*)M, (float*)out, out_ld, out_hs,
+        if (smem > 32 * 1024) cudaFuncSetAttribute(head_matmul_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        mm_launch(head_matmul_kernel<float>, grid, block, smem, s, (const float*)in, in_ld, in_hs, (const float*)M, (float*)out, out_ld, out_hs,
                   n_tokens, K, N);
     } else if (dtype == MM_BF16) {
-        if (smem > 48 * 1024) cudaFuncSetAttribute(head_matmul_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        mm_launch(head_matmul_kernel<__nv_bfloat16>, grid, dim3(128), smem, s, (const __nv_bfloat16*)in, in_ld, in_hs, (const __nv_bfloat16*)M,
+        if (smem > 32 * 1024) cudaFuncSetAttribute(head_matmul_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        mm_launch(head_matmul_kernel<__nv_bfloat16>, grid, block, smem, s, (const __nv_bfloat16*)in, in_ld, in_hs, (const __nv_bfloat16*)M,
                   (__nv_bfloat16*)out, out_ld, out_hs, n_tokens, K, N);
     } else {
         MM_REQUIRE(false, "head product: dtype must be float32 or bfloat16");
