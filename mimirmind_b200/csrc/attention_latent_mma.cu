@@ -5,7 +5,7 @@
 //   s_j = (q . row_j) * scale;  p = softmax_j over the keys j <= position (and inside the window, if one is given);
 //   o = sum_j p_j row_j[0 : rank]
 //
-// One CTA (8 warps) owns a tile of 32 query rows, each row one (token, head) pair of one request; because every head
+// One CTA (8 or 16 warps) owns a tile of 32 or 64 query rows, each row one (token, head) pair of one request; because every head
 // reads the same keys, a key tile is fetched once for all of them.  Keys stream through shared memory in tiles of 32,
 // gathered page by page with cp.async, two stages deep.  Per key tile:
 //
@@ -23,17 +23,17 @@
 
 // query rows per CTA: 32 or 64 (MT 16-row tiles for each of the 2 row groups)
 #define LAT_KEYS 32        // keys per tile
-#define LAT_THREADS 256    // 8 warps: 2 row groups x 4 column groups
 #define LAT_SS 33          // stride of a row of partial scores (floats)
 #define LAT_PS 40          // stride of a row of weights (bfloat16)
 #define LAT_LOG2E 1.4426950408889634f
 
 // 32 cache rows [32][WS] (WS = wide rounded up to 16, + 8); rows outside [lo, hi) and the padding are zero
+template <int THREADS>
 __device__ __forceinline__ void latent_load_keys(__nv_bfloat16* dst, const __nv_bfloat16* __restrict__ pool,
                                                  const int32_t* __restrict__ table, int key0, int lo, int hi, int page_size,
                                                  int page_shift, int wide, int WS) {
     const int chunks = (WS - 8) / 8, real = wide / 8;
-    for (int c = threadIdx.x; c < LAT_KEYS * chunks; c += LAT_THREADS) {
+    for (int c = threadIdx.x; c < LAT_KEYS * chunks; c += THREADS) {
         const int r = c / chunks, part = c - r * chunks;
         const int key = key0 + r;
         __nv_bfloat16* d = dst + r * WS + part * 8;
@@ -49,14 +49,15 @@ __device__ __forceinline__ void latent_load_keys(__nv_bfloat16* dst, const __nv_
 
 // tiles: int32 [n_tiles, 5] = (request, first token row, tokens, first head, heads); row r of the tile is token
 // first + r / heads, head first_head + r % heads; tokens * heads <= 32 MT.  MT: 16-row tiles per warp (a CTA owns 32 MT rows).
-template <int NT, int MT>
-__global__ void __launch_bounds__(LAT_THREADS) attention_latent_kernel(
+template <int NT, int MT, int RG>
+__global__ void __launch_bounds__(RG * 128) attention_latent_kernel(
     const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ pool, __nv_bfloat16* __restrict__ out,
     float* __restrict__ out32, float* __restrict__ part_o, float* __restrict__ part_ml, const int32_t* __restrict__ tiles,
     const int32_t* __restrict__ positions, const int32_t* __restrict__ block_table, int table_width, int page_size, int H,
     int wide, int rank, int window, float scale_log2) {
-    constexpr int ROWS = 32 * MT;                 // query rows of the CTA
-    constexpr int TPR = LAT_THREADS / ROWS;       // threads per row in the softmax stage
+    constexpr int THREADS = RG * 128;             // RG row groups x 4 column groups of one warp each
+    constexpr int ROWS = 16 * MT * RG;            // query rows of the CTA
+    constexpr int TPR = THREADS / ROWS;           // threads per row in the softmax stage
     constexpr int KPT = LAT_KEYS / TPR;           // keys per thread there
     const int WP = (wide + 15) & ~15, WS = WP + 8, KSTEPS = WP / 16;
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -89,7 +90,7 @@ __global__ void __launch_bounds__(LAT_THREADS) attention_latent_kernel(
     if (threadIdx.x < ROWS) sPos[threadIdx.x] = threadIdx.x < n_rows ? positions[tok0 + threadIdx.x / n_heads] : -1;
     {
         const int chunks = WP / 8, real = wide / 8;
-        for (int c = threadIdx.x; c < ROWS * chunks; c += LAT_THREADS) {
+        for (int c = threadIdx.x; c < ROWS * chunks; c += THREADS) {
             const int r = c / chunks, part = c - r * chunks;
             uint4 v = make_uint4(0, 0, 0, 0);
             if (r < n_rows && part < real) {
@@ -101,7 +102,7 @@ __global__ void __launch_bounds__(LAT_THREADS) attention_latent_kernel(
     }
     const int page_shift = (page_size & (page_size - 1)) == 0 ? __ffs(page_size) - 1 : -1;
     if (kt_begin < kt_end)
-        latent_load_keys(sK, pool, table, kt_begin * LAT_KEYS, lo_all, hi_all, page_size, page_shift, wide, WS);
+        latent_load_keys<THREADS>(sK, pool, table, kt_begin * LAT_KEYS, lo_all, hi_all, page_size, page_shift, wide, WS);
     cp_async_commit();
 
     float o[MT][NT][4];
@@ -120,7 +121,7 @@ __global__ void __launch_bounds__(LAT_THREADS) attention_latent_kernel(
         cp_async_wait<0>();
         __syncthreads();                             // tile kt has landed; everyone is done with tile kt - 1
         if (kt + 1 < kt_end) {
-            latent_load_keys(sK + (buf ^ 1) * LAT_KEYS * WS, pool, table, (kt + 1) * LAT_KEYS, lo_all, hi_all, page_size,
+            latent_load_keys<THREADS>(sK + (buf ^ 1) * LAT_KEYS * WS, pool, table, (kt + 1) * LAT_KEYS, lo_all, hi_all, page_size,
                              page_shift, wide, WS);
             cp_async_commit();
         }
@@ -304,10 +305,10 @@ static size_t latent_smem(int wide, int rows) {
 #define LAT_PASS q, pool, out, part_o, part_ml, n_splits, tiles, n_tiles, n_rows, positions, table, table_width, page_size, H, \
                  wide, rank, window, scale, out_f32, s
 
-template <int NT, int MT>
+template <int NT, int MT, int RG>
 static int launch_latent(LAT_ARGS) {
-    const size_t smem = latent_smem(wide, 32 * MT);
-    auto kernel = attention_latent_kernel<NT, MT>;
+    const size_t smem = latent_smem(wide, 16 * MT * RG);
+    auto kernel = attention_latent_kernel<NT, MT, RG>;
     static size_t allowed = 0;                     // per instantiation
     if (smem > allowed) {
         if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
@@ -317,7 +318,7 @@ static int launch_latent(LAT_ARGS) {
         }
         allowed = smem;
     }
-    mm_launch(kernel, dim3(n_tiles, n_splits), dim3(LAT_THREADS), smem, s, (const __nv_bfloat16*)q, (const __nv_bfloat16*)pool,
+    mm_launch(kernel, dim3(n_tiles, n_splits), dim3(RG * 128), smem, s, (const __nv_bfloat16*)q, (const __nv_bfloat16*)pool,
               out_f32 ? nullptr : (__nv_bfloat16*)out, out_f32 ? (float*)out : nullptr, (float*)part_o, (float*)part_ml,
               (const int32_t*)tiles, (const int32_t*)positions, (const int32_t*)table, table_width, page_size, H, wide, rank, window,
               scale * LAT_LOG2E);
@@ -337,7 +338,7 @@ MM_EXPORT int mm_attention_latent_supported(int wide, int rank) {
     return rank >= 16 && rank <= 512 && rank % 16 == 0 && wide >= rank && wide % 8 == 0 && latent_smem(wide, 32) <= LAT_SMEM_MAX;
 }
 
-// the rows of a tile the kernel may be given for this width: 64 where two 16-row tiles per warp fit, else 32
+// the rows of a tile the kernel may be given for this width: 64 (sixteen warps) where that many query rows fit, else 32
 MM_EXPORT int mm_attention_latent_tile_rows(int wide) { return latent_smem(wide, 64) <= LAT_SMEM_MAX ? 64 : 32; }
 
 // q [n, H, wide] and pool [pages, page, wide] bfloat16; out [n, H, rank] bfloat16 or fp32.  tiles int32 [n_tiles, 5] of at
@@ -356,13 +357,13 @@ MM_EXPORT int mm_attention_latent_bf16(const void* q, const void* pool, void* ou
     if (n_tiles == 0) return MM_OK;
     cudaStream_t s = (cudaStream_t)stream;
     if (tile_rows == 64) {
-        if (rank <= 64) return launch_latent<2, 2>(LAT_PASS);
-        if (rank <= 128) return launch_latent<4, 2>(LAT_PASS);
-        if (rank <= 256) return launch_latent<8, 2>(LAT_PASS);
-        return launch_latent<16, 2>(LAT_PASS);
+        if (rank <= 64) return launch_latent<2, 1, 4>(LAT_PASS);
+        if (rank <= 128) return launch_latent<4, 1, 4>(LAT_PASS);
+        if (rank <= 256) return launch_latent<8, 1, 4>(LAT_PASS);
+        return launch_latent<16, 1, 4>(LAT_PASS);
     }
-    if (rank <= 64) return launch_latent<2, 1>(LAT_PASS);
-    if (rank <= 128) return launch_latent<4, 1>(LAT_PASS);
-    if (rank <= 256) return launch_latent<8, 1>(LAT_PASS);
-    return launch_latent<16, 1>(LAT_PASS);
+    if (rank <= 64) return launch_latent<2, 1, 2>(LAT_PASS);
+    if (rank <= 128) return launch_latent<4, 1, 2>(LAT_PASS);
+    if (rank <= 256) return launch_latent<8, 1, 2>(LAT_PASS);
+    return launch_latent<16, 1, 2>(LAT_PASS);
 }
