@@ -94,6 +94,45 @@ __global__ void causal_conv_tokens_kernel(const float* __restrict__ x, int ld, i
     y[(size_t)t * ldy + c] = act ? ls_silu(acc) : acc;
 }
 
+// The same per (token, 4 consecutive channels): a block owns 8 consecutive tokens x 128 channels, so the rows that
+// neighbouring tokens share are read from DRAM once and from L1 after that; 16-byte loads and stores.  A channel's
+// products are summed in the same order as above, so both forms give the same bits.
+template <int K>
+__global__ void __launch_bounds__(256) causal_conv_tokens4_kernel(
+    const float* __restrict__ x, int ld, int C, const float* __restrict__ taps, const float* __restrict__ tail,
+    long long tail_stride, float* __restrict__ y, int ldy, const int32_t* __restrict__ token_req, const int32_t* __restrict__ req_meta,
+    const int32_t* __restrict__ slots, const int32_t* __restrict__ positions, int act, int n_tokens) {
+    const int c = (blockIdx.x * 32 + (threadIdx.x & 31)) * 4;
+    const int t = blockIdx.y * 8 + (threadIdx.x >> 5);
+    if (c >= C || t >= n_tokens) return;
+    const int r = token_req[t];
+    const int o = t - (req_meta ? req_meta[4 * r] : t);       // the token's place in its portion
+    const int pos = positions[t];
+    const float* tl = tail + (size_t)slots[r] * tail_stride;
+    float4 in[K];                                              // every load is issued before the first product
+#pragma unroll
+    for (int j = 0; j < K; ++j) {
+        in[j] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);           // before the sequence's start: zeros (a product with zero adds nothing)
+        if (pos - j >= 0)
+            in[j] = (o - j >= 0) ? *reinterpret_cast<const float4*>(x + (size_t)(t - j) * ld + c)
+                                 : *reinterpret_cast<const float4*>(tl + (size_t)(j - o - 1) * C + c);
+    }
+    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+    for (int j = 0; j < K; ++j) {
+        const float* w = taps + (size_t)c * K + (K - 1 - j);
+        acc[0] = fmaf(w[0], in[j].x, acc[0]);
+        acc[1] = fmaf(w[K], in[j].y, acc[1]);
+        acc[2] = fmaf(w[2 * K], in[j].z, acc[2]);
+        acc[3] = fmaf(w[3 * K], in[j].w, acc[3]);
+    }
+    if (act) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc[e] = ls_silu(acc[e]);
+    }
+    *reinterpret_cast<float4*>(y + (size_t)t * ldy + c) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+}
+
 __global__ void causal_conv_tail_kernel(const float* __restrict__ x, int ld, int C, int K, float* __restrict__ tail, long long tail_stride,
                                         const int32_t* __restrict__ req_meta, const int32_t* __restrict__ slots,
                                         const int32_t* __restrict__ positions) {
@@ -122,9 +161,25 @@ MM_EXPORT int mm_causal_conv_tokens(const void* x, int ld, int C, const void* ta
     MM_REQUIRE((tail != nullptr || K == 1) && slots != nullptr && positions != nullptr && token_req != nullptr && y != nullptr && y != x,
                "causal conv: the state, the positions, the tokens' requests and a result buffer of its own are needed");
     if (n_tokens <= 0 || n_requests <= 0) return MM_OK;
-    mm_launch(causal_conv_tokens_kernel, dim3(ceil_div((long long)n_tokens * C, 256)), dim3(256), 0, (cudaStream_t)stream, (const float*)x, ld, C,
-              (const float*)taps, K, (const float*)tail, tail_stride, (float*)y, ldy, (const int32_t*)token_req, (const int32_t*)req_meta,
-              (const int32_t*)slots, (const int32_t*)positions, act, n_tokens);
+    const bool by4 = C % 4 == 0 && ld % 4 == 0 && ldy % 4 == 0 && tail_stride % 4 == 0 && ceil_div(n_tokens, 8) <= 65535 &&
+                     (((uintptr_t)x | (uintptr_t)y | (uintptr_t)tail) & 15) == 0;
+    if (by4) {
+#define CONV4_CASE(KK)                                                                                                                  \
+    case KK:                                                                                                                            \
+        mm_launch(causal_conv_tokens4_kernel<KK>, dim3(ceil_div(C, 128), ceil_div(n_tokens, 8)), dim3(256), 0, (cudaStream_t)stream,     \
+                  (const float*)x, ld, C, (const float*)taps, (const float*)tail, tail_stride, (float*)y, ldy, (const int32_t*)token_req, \
+                  (const int32_t*)req_meta, (const int32_t*)slots, (const int32_t*)positions, act, n_tokens);                            \
+        break;
+        switch (K) {
+            CONV4_CASE(1) CONV4_CASE(2) CONV4_CASE(3) CONV4_CASE(4) CONV4_CASE(5) CONV4_CASE(6) CONV4_CASE(7) CONV4_CASE(8)
+            default: break;
+        }
+#undef CONV4_CASE
+    } else {
+        mm_launch(causal_conv_tokens_kernel, dim3(ceil_div((long long)n_tokens * C, 256)), dim3(256), 0, (cudaStream_t)stream, (const float*)x, ld, C,
+                  (const float*)taps, K, (const float*)tail, tail_stride, (float*)y, ldy, (const int32_t*)token_req, (const int32_t*)req_meta,
+                  (const int32_t*)slots, (const int32_t*)positions, act, n_tokens);
+    }
     MM_CHECK_LAUNCH();
     if (K > 1) {
         mm_launch(causal_conv_tail_kernel, dim3(ceil_div(C, 128), n_requests), dim3(128), 0, (cudaStream_t)stream, (const float*)x, ld, C, K,
