@@ -5,23 +5,24 @@
 //   s_j = (q . row_j) * scale;  p = softmax_j over the keys j <= position (and inside the window, if one is given);
 //   o = sum_j p_j row_j[0 : rank]
 //
-// One CTA (8 or 16 warps) owns a tile of 32 or 64 query rows, each row one (token, head) pair of one request; because every head
-// reads the same keys, a key tile is fetched once for all of them.  Keys stream through shared memory in tiles of 32,
+// One CTA (8 or 16 warps: 2 or 4 row groups of 4 warps) owns a tile of 32 or 64 query rows, each row one (token, head)
+// pair of one request; because every head reads the same keys, a key tile is fetched once for all of them.  Keys stream through shared memory in tiles of 32,
 // gathered page by page with cp.async, two stages deep.  Per key tile:
 //
 //   1. scores: warp (rg, cg) multiplies the 16 query rows of row group rg with the 32 keys over every fourth 16-wide
 //      slice of `wide` (slices cg, cg + 4, ...) and leaves its partial sums in shared memory;
 //   2. softmax: eight threads per row add the four partial sums, scale and mask them, keep the running maximum and
 //      mass of the row in registers, and leave the weights (bfloat16) and the row's rescale factor in shared memory;
-//   3. values: warp (rg, cg) multiplies the weights of its 16 rows with columns [cg * 8 NT * ..) of the same key tile
-//      (read transposed with ldmatrix) into its fp32 accumulators, NT n-tiles of 8 columns per warp (rank <= 32 NT).
+//   3. values: warp (rg, cg) multiplies the weights of its 16 rows with the columns [cg * 8 NT, (cg + 1) * 8 NT) of the
+//      same key tile (read transposed with ldmatrix) into its fp32 accumulators, NT n-tiles of 8 columns per warp
+//      (rank <= 32 NT).
+// Stages 1 to 3 exchange data inside a row group only, so they are separated by a barrier of the group's four warps.
 //
 // The key tiles of a query tile may be shared out over several CTAs (blockIdx.y); their partial results then go
 // through scratch memory and a merge launch.  Positions come from the device, so a captured step replays with new ones.
 #include "common.cuh"
 #include "mma_sync.cuh"
 
-// query rows per CTA: 32 or 64 (MT 16-row tiles for each of the 2 row groups)
 #define LAT_KEYS 32        // keys per tile
 #define LAT_SS 33          // stride of a row of partial scores (floats)
 #define LAT_PS 40          // stride of a row of weights (bfloat16)
@@ -46,6 +47,12 @@ __device__ __forceinline__ void latent_load_keys(__nv_bfloat16* dst, const __nv_
         }
     }
 }
+
+// A barrier of the four warps of one row group (named barrier 1 + group): the partial scores, the weights and the
+// rescale factors of a row are written and read inside its group only (the softmax threads of a group's rows are the
+// group's own 128 threads), so the groups need not wait for one another between the stages of a key tile and one
+// group's products overlap another's softmax.
+__device__ __forceinline__ void group_sync(int group) { asm volatile("bar.sync %0, 128;" ::"r"(group + 1) : "memory"); }
 
 // tiles: int32 [n_tiles, 5] = (request, first token row, tokens, first head, heads); row r of the tile is token
 // first + r / heads, head first_head + r % heads; tokens * heads <= 32 MT.  MT: 16-row tiles per warp (a CTA owns 32 MT rows).
@@ -163,7 +170,7 @@ __global__ void __launch_bounds__(RG * 128) attention_latent_kernel(
                 }
             }
         }
-        __syncthreads();
+        group_sync(rg);
         // 2. softmax of the tile's scores, row by row
         {
             const int pos = sPos[srow];
@@ -197,7 +204,7 @@ __global__ void __launch_bounds__(RG * 128) attention_latent_kernel(
                 *reinterpret_cast<uint2*>(sP + srow * LAT_PS + skey + e) = make_uint2(pack_bf16(sc[e], sc[e + 1]), pack_bf16(sc[e + 2], sc[e + 3]));
             if (threadIdx.x % TPR == 0) sAlpha[srow] = alpha;
         }
-        __syncthreads();
+        group_sync(rg);
         // 3. the weights times the leading `rank` numbers of the same rows
         {
 #pragma unroll
