@@ -33,17 +33,22 @@ template <int THREADS>
 __device__ __forceinline__ void latent_load_keys(__nv_bfloat16* dst, const __nv_bfloat16* __restrict__ pool,
                                                  const int32_t* __restrict__ table, int key0, int lo, int hi, int page_size,
                                                  int page_shift, int wide, int WS) {
+    // a warp per row (one page lookup per row), a lane per 16-byte piece
     const int chunks = (WS - 8) / 8, real = wide / 8;
-    for (int c = threadIdx.x; c < LAT_KEYS * chunks; c += THREADS) {
-        const int r = c / chunks, part = c - r * chunks;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int r = warp; r < LAT_KEYS; r += THREADS / 32) {
         const int key = key0 + r;
-        __nv_bfloat16* d = dst + r * WS + part * 8;
-        if (key >= lo && key < hi && part < real) {
+        const bool ok = key >= lo && key < hi;
+        const __nv_bfloat16* src = pool;
+        if (ok) {
             const int pidx = page_shift >= 0 ? (key >> page_shift) : (key / page_size);
             const int slot = key - pidx * page_size;
-            cp_async16(d, pool + ((size_t)table[pidx] * page_size + slot) * wide + part * 8);
-        } else {
-            *reinterpret_cast<uint4*>(d) = make_uint4(0, 0, 0, 0);
+            src = pool + ((size_t)table[pidx] * page_size + slot) * wide;
+        }
+        __nv_bfloat16* d = dst + r * WS;
+        for (int part = lane; part < chunks; part += 32) {
+            if (ok && part < real) cp_async16(d + part * 8, src + part * 8);
+            else *reinterpret_cast<uint4*>(d + part * 8) = make_uint4(0, 0, 0, 0);
         }
     }
 }
@@ -210,9 +215,12 @@ __global__ void __launch_bounds__(RG * 128) attention_latent_kernel(
 #pragma unroll
             for (int mt = 0; mt < MT; ++mt) {
                 const float a_lo = sAlpha[row_base + mt * 16 + (lane >> 2)], a_hi = sAlpha[row_base + mt * 16 + 8 + (lane >> 2)];
+                // a factor of 1 (no row of the warp met a new maximum in this tile) changes nothing
+                if (__any_sync(0xffffffffu, a_lo != 1.0f || a_hi != 1.0f)) {
 #pragma unroll
-                for (int j = 0; j < NT; ++j) {
-                    o[mt][j][0] *= a_lo; o[mt][j][1] *= a_lo; o[mt][j][2] *= a_hi; o[mt][j][3] *= a_hi;
+                    for (int j = 0; j < NT; ++j) {
+                        o[mt][j][0] *= a_lo; o[mt][j][1] *= a_lo; o[mt][j][2] *= a_hi; o[mt][j][3] *= a_hi;
+                    }
                 }
             }
 #pragma unroll
