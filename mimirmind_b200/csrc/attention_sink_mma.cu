@@ -24,35 +24,41 @@
 #define SDEC_STAGES 3
 
 // 64 key rows [64][DK + 8] and the same 64 value rows [64][DV + 8] of one KV head; rows outside [lo, hi) are zero.
+// Warp w fetches rows 16 w .. 16 w + 15: its first sixteen lanes look up one row's page and place each, and every lane
+// takes those from the row's lane for the 16-byte pieces it copies (one table read per row, not per piece).  Every
+// thread of the CTA must call this together.
 template <int DK, int DV>
 __device__ __forceinline__ void load_kv_tile2(__nv_bfloat16* dK, __nv_bfloat16* dV, const __nv_bfloat16* __restrict__ kpool,
                                               const __nv_bfloat16* __restrict__ vpool, const int32_t* __restrict__ table,
                                               int key0, int lo, int hi, int G, int g, int page_size, int page_shift, int Gv) {
     constexpr int KS = DK + 8, VS = DV + 8, KC = DK / 8, VC = DV / 8;
+    static_assert(SATT_THREADS == 128 && SKT == 64 && (16 * KC) % 32 == 0 && (16 * VC) % 32 == 0, "a warp per 16 rows");
     const int gv = g % Gv;      // the value pool has Gv heads; key head g reads value head g mod Gv
-    for (int c = threadIdx.x; c < SKT * KC; c += SATT_THREADS) {
-        const int r = c / KC, part = c - r * KC;
-        const int key = key0 + r;
-        __nv_bfloat16* d = dK + r * KS + part * 8;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    int page = -1, slot = 0;
+    {
+        const int key = key0 + warp * 16 + (lane & 15);
         if (key >= lo && key < hi) {
             const int pidx = page_shift >= 0 ? (key >> page_shift) : (key / page_size);
-            const int slot = key - pidx * page_size;
-            cp_async16(d, kpool + (((size_t)table[pidx] * G + g) * page_size + slot) * DK + part * 8);
-        } else {
-            *reinterpret_cast<uint4*>(d) = make_uint4(0, 0, 0, 0);
+            slot = key - pidx * page_size;
+            page = table[pidx];
         }
     }
-    for (int c = threadIdx.x; c < SKT * VC; c += SATT_THREADS) {
-        const int r = c / VC, part = c - r * VC;
-        const int key = key0 + r;
-        __nv_bfloat16* d = dV + r * VS + part * 8;
-        if (key >= lo && key < hi) {
-            const int pidx = page_shift >= 0 ? (key >> page_shift) : (key / page_size);
-            const int slot = key - pidx * page_size;
-            cp_async16(d, vpool + (((size_t)table[pidx] * Gv + gv) * page_size + slot) * DV + part * 8);
-        } else {
-            *reinterpret_cast<uint4*>(d) = make_uint4(0, 0, 0, 0);
-        }
+#pragma unroll
+    for (int i = 0; i < 16 * KC / 32; ++i) {
+        const int c = i * 32 + lane, r = c / KC, part = c - r * KC;
+        const int p = __shfl_sync(0xffffffffu, page, r), sl = __shfl_sync(0xffffffffu, slot, r);
+        __nv_bfloat16* d = dK + (warp * 16 + r) * KS + part * 8;
+        if (p >= 0) cp_async16(d, kpool + (((size_t)p * G + g) * page_size + sl) * DK + part * 8);
+        else *reinterpret_cast<uint4*>(d) = make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int i = 0; i < 16 * VC / 32; ++i) {
+        const int c = i * 32 + lane, r = c / VC, part = c - r * VC;
+        const int p = __shfl_sync(0xffffffffu, page, r), sl = __shfl_sync(0xffffffffu, slot, r);
+        __nv_bfloat16* d = dV + (warp * 16 + r) * VS + part * 8;
+        if (p >= 0) cp_async16(d, vpool + (((size_t)p * Gv + gv) * page_size + sl) * DV + part * 8);
+        else *reinterpret_cast<uint4*>(d) = make_uint4(0, 0, 0, 0);
     }
 }
 
