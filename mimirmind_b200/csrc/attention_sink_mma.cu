@@ -360,8 +360,11 @@ __global__ void __launch_bounds__(SATT_THREADS) attention_sink_decode_kernel(
                     const int key = key0 + j * 8 + (lane & 3) * 2 + (e & 1);
                     float v = -INFINITY;
                     if (key >= k_begin && key < k_end) {
-                        v = softcap > 0.0f ? tanhf(s[j][e] * cap_in) * cap_out : s[j][e] * scale_log2;
-                        // rows of the tile are the query heads of this kv head: the bias of (distance, head)
+                        // rows of the tile are the query heads of this kv head; the rows beyond them hold zero queries and
+                        // scores, whose capped form is zero as well
+                        const bool real_row = (lane >> 2) + (e >= 2 ? 8 : 0) < qpg;
+                        v = softcap > 0.0f ? (real_row ? tanhf(s[j][e] * cap_in) * cap_out : 0.0f) : s[j][e] * scale_log2;
+                        // the bias of (distance, head)
                         const int hq = g * qpg + (lane >> 2) + (e >= 2 ? 8 : 0);
                         if (dist_bias != nullptr && hq < H) v += dist_bias[(size_t)hq * (dist_max + 1) + min(pos - key, dist_max)] * SINK_LOG2E_F;
                     }
