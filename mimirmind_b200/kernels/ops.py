@@ -1337,7 +1337,7 @@ def head_matmul(x: torch.Tensor, matrices: torch.Tensor, out: torch.Tensor, head
         raise KernelError("head product: shape mismatch")
     if x.dtype != matrices.dtype or out.dtype != x.dtype or not matrices.is_contiguous() or x.stride(1) != 1 or out.stride(1) != 1:
         raise KernelError("head product: one dtype and unit column strides are needed")
-    if x.dtype == torch.bfloat16 and n >= HEAD_MATMUL_LIBRARY_FROM:
+    if x.dtype == torch.bfloat16 and n >= HEAD_MATMUL_LIBRARY_FROM and x.is_contiguous() and out.is_contiguous():
         # a portion of a prompt: one batched product of the vendor library over the heads, operands and result in place
         wide = out.shape[1] // H
         torch.bmm(x.view(n, H, K).transpose(0, 1), matrices, out=out.view(n, H, wide)[:, :, :N].transpose(0, 1))
