@@ -64,6 +64,27 @@ __device__ __forceinline__ float from_f32<float>(float v) { return v; }
 template <>
 __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
 
+// ---- gated activations of a two-matrix feed-forward ---------------------------------------------------------------------
+// g, u: the gate's and the up projection's values, both multiplied by `s` first (a weight on the input of the layer
+// passes through both products).  act 0: silu(g) u.  act 1, the clamped form: g <- min(g, limit), u <- clamp(u, -limit,
+// limit), g sigmoid(1.702 g) (u + 1).  FAST: __expf.
+#define MM_GLU_SILU 0
+#define MM_GLU_CLAMPED 1
+#define MM_GLU_CLAMPED_ALPHA 1.702f
+template <bool FAST>
+__device__ __forceinline__ float glu_act(float g, float u, int act, float limit, float s) {
+    g *= s;
+    u *= s;
+    if (act == MM_GLU_CLAMPED) {
+        g = fminf(g, limit);
+        u = fminf(fmaxf(u, -limit), limit);
+        const float e = FAST ? __expf(-MM_GLU_CLAMPED_ALPHA * g) : expf(-MM_GLU_CLAMPED_ALPHA * g);
+        return g / (1.0f + e) * (u + 1.0f);
+    }
+    const float e = FAST ? __expf(-g) : expf(-g);
+    return g / (1.0f + e) * u;
+}
+
 // ---- reductions --------------------------------------------------------------
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll

@@ -614,3 +614,143 @@ MM_EXPORT int mm_linear_state_chunked(const void* q, const void* k, const void* 
     }
     return MM_OK;
 }
+
+// ---------------------------------------------------------------------------------------------------------------
+// a forget gate per key channel whose complement is the write strength (HGRN2)
+// ---------------------------------------------------------------------------------------------------------------
+//   f_t = l + (1 - l) sigmoid(z_t + b)    per head and key channel, with a lower bound l per channel;
+//   S_t = diag(f_t) S_(t-1) + (1 - f_t) v_t^T;    o_t = S_t^T q_t.
+// The key of the general recurrence is tied to the decay, which is a vector over the rows of S instead of one number.
+//
+// Between the projection and the recurrence, in place on the fp32 rows x [n, ld]: act_q (1: silu) on the n_qf numbers at
+// q_off, and the n_qf numbers at f_off become the forget gate from the bias and the lower bound (fp32 [n_qf], bias null: 0).
+__global__ void forget_gate_prep_kernel(float* __restrict__ x, int ld, long long total, int q_off, int f_off, int n_qf, int act_q,
+                                        const float* __restrict__ bias, const float* __restrict__ lower) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const long long t = i / n_qf;
+    const int c = (int)(i - t * n_qf);
+    float* row = x + (size_t)t * ld;
+    if (act_q) row[q_off + c] = ls_silu(row[q_off + c]);
+    const float l = lower ? lower[c] : 0.0f;
+    row[f_off + c] = l + (1.0f - l) * ls_sigmoid(row[f_off + c] + (bias ? bias[c] : 0.0f));
+}
+
+MM_EXPORT int mm_forget_gate_prep(void* x, int ld, int n_tokens, int q_off, int f_off, int n_qf, int act_q, const void* bias, const void* lower,
+                                  void* stream) {
+    MM_REQUIRE(n_tokens >= 0 && n_qf > 0 && q_off >= 0 && f_off >= 0 && q_off + n_qf <= ld && f_off + n_qf <= ld, "forget gate: columns outside the row");
+    if (n_tokens == 0) return MM_OK;
+    const long long total = (long long)n_tokens * n_qf;
+    mm_launch(forget_gate_prep_kernel, dim3(ceil_div(total, 256)), dim3(256), 0, (cudaStream_t)stream, (float*)x, ld, total, q_off, f_off, n_qf, act_q,
+              (const float*)bias, (const float*)lower);
+    MM_CHECK_LAUNCH();
+    return MM_OK;
+}
+
+// The walk: q, f fp32 rows with H heads of dk (row strides ldq, ldf), v with H heads of dv.  A block of 8 warps owns 32
+// columns of one head's S for one request, a warp four of them, a lane the entries lane, lane + 32, ... of each; q, f and
+// v of FG_AHEAD tokens at a time are staged in shared memory.  The state's layout in a slot is [H, dv, dk], as in the walk
+// above; a request at position 0 starts from zero whatever its slot holds.
+#define FG_AHEAD 16
+#define FG_COLS 32
+template <int PER>
+__global__ void __launch_bounds__(256) forget_gate_walk_kernel(const float* __restrict__ q, const float* __restrict__ f, const float* __restrict__ v,
+                                                               int ldq, int ldf, int ldv, float* __restrict__ out, float* __restrict__ state,
+                                                               long long state_stride, const int32_t* __restrict__ req_meta,
+                                                               const int32_t* __restrict__ slots, const int32_t* __restrict__ positions, int H,
+                                                               int dk, int dv) {
+    extern __shared__ float fg_smem[];
+    float* sq = fg_smem;                          // [AHEAD][dk]
+    float* sf = sq + FG_AHEAD * dk;               // [AHEAD][dk]
+    float* sv = sf + FG_AHEAD * dk;               // [AHEAD][COLS]
+    float* so = sv + FG_AHEAD * FG_COLS;          // [AHEAD][COLS]
+    const int h = blockIdx.y, r = blockIdx.z, col0 = blockIdx.x * FG_COLS;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t0 = req_meta ? req_meta[4 * r] : r;
+    const int n = req_meta ? req_meta[4 * r + 1] : 1;
+    const bool fresh = positions[t0] == 0;
+    float* st = state + (size_t)slots[r] * state_stride + (size_t)h * dv * dk;
+    float S[4][PER];
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+        const int col = col0 + warp * 4 + c;
+#pragma unroll
+        for (int e = 0; e < PER; ++e) {
+            const int i = lane + 32 * e;
+            S[c][e] = (!fresh && col < dv && i < dk) ? st[(size_t)col * dk + i] : 0.0f;
+        }
+    }
+    for (int base = 0; base < n; base += FG_AHEAD) {
+        const int cnt = min(FG_AHEAD, n - base);
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < cnt * dk; idx += 256) {
+            const int tt = idx / dk, i = idx - tt * dk;
+            const size_t t = (size_t)(t0 + base + tt);
+            sq[idx] = q[t * ldq + h * dk + i];
+            sf[idx] = f[t * ldf + h * dk + i];
+        }
+        for (int idx = threadIdx.x; idx < cnt * FG_COLS; idx += 256) {
+            const int tt = idx / FG_COLS, c = idx - tt * FG_COLS;
+            sv[idx] = col0 + c < dv ? v[(size_t)(t0 + base + tt) * ldv + h * dv + col0 + c] : 0.0f;
+        }
+        __syncthreads();
+        for (int tt = 0; tt < cnt; ++tt) {
+            float qq[PER], ff[PER];
+#pragma unroll
+            for (int e = 0; e < PER; ++e) {
+                const int i = lane + 32 * e;
+                qq[e] = i < dk ? sq[tt * dk + i] : 0.0f;
+                ff[e] = i < dk ? sf[tt * dk + i] : 1.0f;
+            }
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const float vv = sv[tt * FG_COLS + warp * 4 + c];
+                float dot = 0.0f;
+#pragma unroll
+                for (int e = 0; e < PER; ++e) {
+                    S[c][e] = fmaf(ff[e], S[c][e], (1.0f - ff[e]) * vv);
+                    dot = fmaf(S[c][e], qq[e], dot);
+                }
+                dot = warp_sum(dot);
+                if (lane == 0) so[tt * FG_COLS + warp * 4 + c] = dot;
+            }
+        }
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < cnt * FG_COLS; idx += 256) {
+            const int tt = idx / FG_COLS, c = idx - tt * FG_COLS;
+            if (col0 + c < dv) out[(size_t)(t0 + base + tt) * H * dv + h * dv + col0 + c] = so[idx];
+        }
+    }
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+        const int col = col0 + warp * 4 + c;
+        if (col >= dv) continue;
+#pragma unroll
+        for (int e = 0; e < PER; ++e) {
+            const int i = lane + 32 * e;
+            if (i < dk) st[(size_t)col * dk + i] = S[c][e];
+        }
+    }
+}
+
+MM_EXPORT int mm_forget_gate_walk(const void* q, const void* f, const void* v, int ldq, int ldf, int ldv, void* out, void* state,
+                                  long long state_stride, const void* req_meta, const void* slots, const void* positions, int n_requests, int H,
+                                  int dk, int dv, void* stream) {
+    MM_REQUIRE(H > 0 && dk > 0 && dv > 0, "forget gate walk: bad sizes");
+    MM_REQUIRE(dk <= 256, "forget gate walk: key sizes above 256 are not supported");
+    MM_REQUIRE(state != nullptr && slots != nullptr && positions != nullptr, "forget gate walk: the state and the positions are needed");
+    if (n_requests <= 0) return MM_OK;
+    const dim3 grid(ceil_div(dv, FG_COLS), H, n_requests);
+    const size_t smem = sizeof(float) * FG_AHEAD * (2 * (size_t)dk + 2 * FG_COLS);
+    cudaStream_t s = (cudaStream_t)stream;
+#define FG_LAUNCH(PER)                                                                                                                          \
+    mm_launch(forget_gate_walk_kernel<PER>, grid, dim3(256), smem, s, (const float*)q, (const float*)f, (const float*)v, ldq, ldf, ldv, (float*)out, \
+              (float*)state, state_stride, (const int32_t*)req_meta, (const int32_t*)slots, (const int32_t*)positions, H, dk, dv)
+    if (dk <= 32) FG_LAUNCH(1);
+    else if (dk <= 64) FG_LAUNCH(2);
+    else if (dk <= 128) FG_LAUNCH(4);
+    else FG_LAUNCH(8);
+#undef FG_LAUNCH
+    MM_CHECK_LAUNCH();
+    return MM_OK;
+}

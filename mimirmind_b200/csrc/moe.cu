@@ -29,20 +29,25 @@ __device__ __forceinline__ void warp_argmax(float& v, int& i) {      // the larg
 }
 
 // One warp: the choice for one token from its E logits `zr`; s, gs: the warp's scratch (E and `groups` floats).
+// scoring 0: s = softmax(z), the chosen weights divided by their sum; 1: s = sigmoid(z), the chosen weights as they are.
 __device__ __forceinline__ void moe_route_warp(const float* zr, float* s, float* gs, int lane, int E, int top, int groups, int keep,
-                                               int32_t* __restrict__ idx, float* __restrict__ wts, size_t t) {
-    float m = -INFINITY;
-    for (int e = lane; e < E; e += 32) m = fmaxf(m, zr[e]);
-    m = warp_max(m);
-    float sum = 0.0f;
-    for (int e = lane; e < E; e += 32) {
-        const float p = expf(zr[e] - m);
-        s[e] = p;
-        sum += p;
+                                               int32_t* __restrict__ idx, float* __restrict__ wts, size_t t, int scoring = 0) {
+    if (scoring == 1) {
+        for (int e = lane; e < E; e += 32) s[e] = 1.0f / (1.0f + expf(-zr[e]));
+    } else {
+        float m = -INFINITY;
+        for (int e = lane; e < E; e += 32) m = fmaxf(m, zr[e]);
+        m = warp_max(m);
+        float sum = 0.0f;
+        for (int e = lane; e < E; e += 32) {
+            const float p = expf(zr[e] - m);
+            s[e] = p;
+            sum += p;
+        }
+        sum = warp_sum(sum);
+        const float inv = 1.0f / sum;
+        for (int e = lane; e < E; e += 32) s[e] *= inv;
     }
-    sum = warp_sum(sum);
-    const float inv = 1.0f / sum;
-    for (int e = lane; e < E; e += 32) s[e] *= inv;
     __syncwarp();
     const int size = E / groups;
     if (keep < groups) {
@@ -93,20 +98,20 @@ __device__ __forceinline__ void moe_route_warp(const float* zr, float* s, float*
         }
     }
     __syncwarp();
-    if (lane == 0) {
+    if (lane == 0 && scoring == 0) {
         const float d = total + 1e-20f;
         for (int kk = 0; kk < top; ++kk) wts[t * top + kk] /= d;
     }
 }
 
 __global__ void moe_route_kernel(const float* __restrict__ z, int ldz, int n_tokens, int E, int top, int groups, int keep,
-                                 int32_t* __restrict__ idx, float* __restrict__ wts) {
+                                 int32_t* __restrict__ idx, float* __restrict__ wts, int scoring) {
     extern __shared__ float route_smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
     const int t = blockIdx.x * warps + warp;
     if (t >= n_tokens) return;
     float* s = route_smem + (size_t)warp * (E + groups);
-    moe_route_warp(z + (size_t)t * ldz, s, s + E, lane, E, top, groups, keep, idx, wts, (size_t)t);
+    moe_route_warp(z + (size_t)t * ldz, s, s + E, lane, E, top, groups, keep, idx, wts, (size_t)t, scoring);
 }
 
 // The router's product and its choice in one launch, one block per token: every warp takes experts in turn and sums
@@ -132,7 +137,7 @@ __device__ __forceinline__ void load8<__nv_bfloat16>(const __nv_bfloat16* p, flo
 
 template <typename T>
 __global__ void __launch_bounds__(256) moe_router_kernel(const T* __restrict__ x, int ldx, const float* __restrict__ w, int D, int E, int top,
-                                                         int groups, int keep, int vec, int32_t* __restrict__ idx, float* __restrict__ wts) {
+                                                         int groups, int keep, int vec, int32_t* __restrict__ idx, float* __restrict__ wts, int scoring) {
     extern __shared__ float route_smem[];      // logits [E], scores [E], runs [groups]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const size_t t = blockIdx.x;
@@ -161,11 +166,12 @@ __global__ void __launch_bounds__(256) moe_router_kernel(const T* __restrict__ x
         if (lane == 0) route_smem[e] = acc;
     }
     __syncthreads();
-    if (warp == 0) moe_route_warp(route_smem, route_smem + E, route_smem + 2 * E, lane, E, top, groups, keep, idx, wts, t);
+    if (warp == 0) moe_route_warp(route_smem, route_smem + E, route_smem + 2 * E, lane, E, top, groups, keep, idx, wts, t, scoring);
 }
 
-MM_EXPORT int mm_moe_router(const void* x, int x_dtype, int ldx, const void* w, int n_tokens, int D, int E, int top, int groups, int keep,
-                            void* idx, void* wts, void* stream) {
+MM_EXPORT int mm_moe_router_scored(const void* x, int x_dtype, int ldx, const void* w, int n_tokens, int D, int E, int top, int groups, int keep,
+                                   int scoring, void* idx, void* wts, void* stream) {
+    MM_REQUIRE(scoring == 0 || scoring == 1, "moe router: the scoring is 0 (softmax, renormed) or 1 (sigmoid, as it is)");
     MM_REQUIRE(n_tokens >= 0 && D > 0 && ldx >= D && E > 0 && top > 0 && top <= E && groups > 0 && E % groups == 0 && keep > 0 && keep <= groups,
                "moe router: experts must split into equal runs, and 0 < top <= experts, 0 < keep <= runs");
     MM_REQUIRE((size_t)(2 * E + groups) * sizeof(float) <= 48 * 1024, "moe router: too many experts for the router's shared memory");
@@ -174,14 +180,19 @@ MM_EXPORT int mm_moe_router(const void* x, int x_dtype, int ldx, const void* w, 
     const int vec = D % 8 == 0 && ldx % 8 == 0 && (((uintptr_t)x | (uintptr_t)w) & 15) == 0;
     if (x_dtype == MM_F32)
         mm_launch(moe_router_kernel<float>, dim3(n_tokens), dim3(256), smem, (cudaStream_t)stream, (const float*)x, ldx, (const float*)w, D, E, top,
-                  groups, keep, vec, (int32_t*)idx, (float*)wts);
+                  groups, keep, vec, (int32_t*)idx, (float*)wts, scoring);
     else if (x_dtype == MM_BF16)
         mm_launch(moe_router_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(256), smem, (cudaStream_t)stream, (const __nv_bfloat16*)x, ldx,
-                  (const float*)w, D, E, top, groups, keep, vec, (int32_t*)idx, (float*)wts);
+                  (const float*)w, D, E, top, groups, keep, vec, (int32_t*)idx, (float*)wts, scoring);
     else
         MM_REQUIRE(false, "moe router: dtype must be float32 or bfloat16");
     MM_CHECK_LAUNCH();
     return MM_OK;
+}
+
+MM_EXPORT int mm_moe_router(const void* x, int x_dtype, int ldx, const void* w, int n_tokens, int D, int E, int top, int groups, int keep,
+                            void* idx, void* wts, void* stream) {
+    return mm_moe_router_scored(x, x_dtype, ldx, w, n_tokens, D, E, top, groups, keep, 0, idx, wts, stream);
 }
 
 MM_EXPORT int mm_moe_route(const void* z, int ldz, int n_tokens, int E, int top, int groups, int keep, void* idx, void* wts, void* stream) {
@@ -191,7 +202,7 @@ MM_EXPORT int mm_moe_route(const void* z, int ldz, int n_tokens, int E, int top,
     if (n_tokens == 0) return MM_OK;
     const int warps = 4;
     mm_launch(moe_route_kernel, dim3(ceil_div(n_tokens, warps)), dim3(warps * 32), (size_t)warps * (E + groups) * sizeof(float),
-              (cudaStream_t)stream, (const float*)z, ldz, n_tokens, E, top, groups, keep, (int32_t*)idx, (float*)wts);
+              (cudaStream_t)stream, (const float*)z, ldz, n_tokens, E, top, groups, keep, (int32_t*)idx, (float*)wts, 0);
     MM_CHECK_LAUNCH();
     return MM_OK;
 }
@@ -348,7 +359,7 @@ __device__ __forceinline__ bool moe_tile(const int32_t* __restrict__ offsets, in
 template <typename TA, typename TW, typename TC, bool GATED>
 __global__ void __launch_bounds__(256) moe_gemm_simt_kernel(const TA* __restrict__ A, int lda, const TW* __restrict__ W, TC* __restrict__ C, int ldc,
                                                             const int32_t* __restrict__ offsets, const int32_t* __restrict__ order, int E, int top,
-                                                            int N, int K) {
+                                                            int N, int K, int act, float limit, const float* __restrict__ row_scale) {
     __shared__ float As[MOE_BK][MOE_BM + 4];
     __shared__ float Ws[MOE_BK][MOE_BN + 4];
     __shared__ float Us[GATED ? MOE_BK : 1][MOE_BN + 4];
@@ -428,7 +439,7 @@ __global__ void __launch_bounds__(256) moe_gemm_simt_kernel(const TA* __restrict
             const int n = n0 + tx * 4 + j;
             if (n >= N) continue;
             float v = acc[i][j];
-            if (GATED) v = v / (1.0f + expf(-v)) * up[i][j];
+            if (GATED) v = glu_act<false>(v, up[i][j], act, limit, row_scale ? row_scale[order[lo + m]] : 1.0f);
             C[out_row * ldc + n] = from_f32<TC>(v);
         }
     }
@@ -439,7 +450,8 @@ __global__ void __launch_bounds__(256) moe_gemm_simt_kernel(const TA* __restrict
 template <bool GATED, typename TC>
 __global__ void __launch_bounds__(128) moe_gemm_mma_kernel(const __nv_bfloat16* __restrict__ A, int lda, const __nv_bfloat16* __restrict__ W,
                                                            TC* __restrict__ C, int ldc, const int32_t* __restrict__ offsets,
-                                                           const int32_t* __restrict__ order, int E, int top, int N, int K, int interleaved) {
+                                                           const int32_t* __restrict__ order, int E, int top, int N, int K, int interleaved, int act, float limit,
+                                                           const float* __restrict__ row_scale) {
     // K in steps of 64 through a ring of MOE_STAGES stages: a decode step's tiles hold a handful of rows and stream a
     // whole expert, so what counts is how many bytes of weights a CTA keeps in flight (rows of 144 bytes: ldmatrix
     // reads without bank conflicts)
@@ -555,7 +567,7 @@ __global__ void __launch_bounds__(128) moe_gemm_mma_kernel(const __nv_bfloat16* 
                     const int n = n0 + wn + ni * 8 + (lane & 3) * 2 + c;
                     if (n >= N) continue;
                     float v = acc[mi][ni][half * 2 + c];
-                    if (GATED) v = v / (1.0f + __expf(-v)) * up[mi][ni][half * 2 + c];
+                    if (GATED) v = glu_act<true>(v, up[mi][ni][half * 2 + c], act, limit, row_scale ? row_scale[order[lo + m]] : 1.0f);
                     C[out_row * ldc + n] = from_f32<TC>(v);
                 }
         }
@@ -563,9 +575,15 @@ __global__ void __launch_bounds__(128) moe_gemm_mma_kernel(const __nv_bfloat16* 
 
 // A [rows, lda] (gated: the step's tokens; else the sorted hidden rows), W the experts' stacked matrices, C: gated
 // [n_rows, N] in sorted order, else [n_rows, N] with row order[i] written.  n_rows = tokens * top.
-MM_EXPORT int mm_moe_gemm(const void* A, int a_dtype, int lda, const void* W, int w_dtype, void* C, int c_dtype, int ldc, const void* offsets,
-                          const void* order, int n_rows, int E, int top, int N, int K, int gated, int tensor_cores, int interleaved,
-                          void* stream) {
+// act: what a gated product does with its two halves (glu_act in common.cuh: 0 silu(g) u; 1 the clamped form with
+// `limit`); row_scale [tokens * top] fp32 or null: row (token * top + choice) of a gated product is multiplied by it
+// before the activation (a weight on the expert's input: W (s x) = s (W x)).
+MM_EXPORT int mm_moe_gemm_act(const void* A, int a_dtype, int lda, const void* W, int w_dtype, void* C, int c_dtype, int ldc, const void* offsets,
+                              const void* order, int n_rows, int E, int top, int N, int K, int gated, int tensor_cores, int interleaved,
+                              int act, float limit, const void* row_scale_, void* stream) {
+    const float* row_scale = (const float*)row_scale_;
+    MM_REQUIRE(act == 0 || act == 1, "moe gemm: the activation is 0 (silu) or 1 (clamped)");
+    MM_REQUIRE(gated || (act == 0 && row_scale == nullptr), "moe gemm: activation and row scale belong to the gated product");
     MM_REQUIRE(n_rows >= 0 && E > 0 && top > 0 && N > 0 && K > 0 && lda >= K && ldc >= N, "moe gemm: bad sizes");
     MM_REQUIRE(!interleaved || (gated && N % 8 == 0), "moe gemm: interleaved gate and up rows need a gated product of a multiple of 8 columns");
     if (n_rows == 0) return MM_OK;
@@ -584,11 +602,11 @@ MM_EXPORT int mm_moe_gemm(const void* A, int a_dtype, int lda, const void* W, in
             configured = true;
         }
         if (gated && c_dtype == MM_BF16)
-            mm_launch(moe_gemm_mma_kernel<true, bf>, grid, dim3(128), tile_smem, s, (const bf*)A, lda, (const bf*)W, (bf*)C, ldc, off, ord, E, top, N, K, interleaved);
+            mm_launch(moe_gemm_mma_kernel<true, bf>, grid, dim3(128), tile_smem, s, (const bf*)A, lda, (const bf*)W, (bf*)C, ldc, off, ord, E, top, N, K, interleaved, act, limit, row_scale);
         else if (!gated && c_dtype == MM_BF16)
-            mm_launch(moe_gemm_mma_kernel<false, bf>, grid, dim3(128), tile_smem, s, (const bf*)A, lda, (const bf*)W, (bf*)C, ldc, off, ord, E, top, N, K, 0);
+            mm_launch(moe_gemm_mma_kernel<false, bf>, grid, dim3(128), tile_smem, s, (const bf*)A, lda, (const bf*)W, (bf*)C, ldc, off, ord, E, top, N, K, 0, 0, 0.0f, (const float*)nullptr);
         else if (!gated && c_dtype == MM_F32)
-            mm_launch(moe_gemm_mma_kernel<false, float>, grid, dim3(128), tile_smem, s, (const bf*)A, lda, (const bf*)W, (float*)C, ldc, off, ord, E, top, N, K, 0);
+            mm_launch(moe_gemm_mma_kernel<false, float>, grid, dim3(128), tile_smem, s, (const bf*)A, lda, (const bf*)W, (float*)C, ldc, off, ord, E, top, N, K, 0, 0, 0.0f, (const float*)nullptr);
         else
             MM_REQUIRE(false, "moe gemm: this combination of dtypes is not built");
         MM_CHECK_LAUNCH();
@@ -598,9 +616,9 @@ MM_EXPORT int mm_moe_gemm(const void* A, int a_dtype, int lda, const void* W, in
 #define MOE_SIMT(TA, TW, TC)                                                                                                                  \
     do {                                                                                                                                      \
         if (gated)                                                                                                                            \
-            mm_launch(moe_gemm_simt_kernel<TA, TW, TC, true>, grid, dim3(256), 0, s, (const TA*)A, lda, (const TW*)W, (TC*)C, ldc, off, ord, E, top, N, K); \
+            mm_launch(moe_gemm_simt_kernel<TA, TW, TC, true>, grid, dim3(256), 0, s, (const TA*)A, lda, (const TW*)W, (TC*)C, ldc, off, ord, E, top, N, K, act, limit, row_scale); \
         else                                                                                                                                  \
-            mm_launch(moe_gemm_simt_kernel<TA, TW, TC, false>, grid, dim3(256), 0, s, (const TA*)A, lda, (const TW*)W, (TC*)C, ldc, off, ord, E, top, N, K); \
+            mm_launch(moe_gemm_simt_kernel<TA, TW, TC, false>, grid, dim3(256), 0, s, (const TA*)A, lda, (const TW*)W, (TC*)C, ldc, off, ord, E, top, N, K, 0, 0.0f, (const float*)nullptr); \
     } while (0)
     if (a_dtype == MM_F32 && w_dtype == MM_F32 && c_dtype == MM_F32) MOE_SIMT(float, float, float);
     else if (a_dtype == MM_BF16 && w_dtype == MM_BF16 && c_dtype == MM_BF16) MOE_SIMT(bf, bf, bf);
@@ -609,6 +627,13 @@ MM_EXPORT int mm_moe_gemm(const void* A, int a_dtype, int lda, const void* W, in
 #undef MOE_SIMT
     MM_CHECK_LAUNCH();
     return MM_OK;
+}
+
+MM_EXPORT int mm_moe_gemm(const void* A, int a_dtype, int lda, const void* W, int w_dtype, void* C, int c_dtype, int ldc, const void* offsets,
+                          const void* order, int n_rows, int E, int top, int N, int K, int gated, int tensor_cores, int interleaved,
+                          void* stream) {
+    return mm_moe_gemm_act(A, a_dtype, lda, W, w_dtype, C, c_dtype, ldc, offsets, order, n_rows, E, top, N, K, gated, tensor_cores, interleaved,
+                           0, 0.0f, nullptr, stream);
 }
 
 // out[t, :] = sum over the token's choices c, in order, of wts[t, c] * y[row(t, c), :], row(t, c) = t * top + c or, when
@@ -621,7 +646,7 @@ __global__ void moe_combine_kernel(const TY* __restrict__ y, const float* __rest
         float acc = 0.0f;
         for (int c = 0; c < top; ++c) {
             const size_t row = place ? (size_t)place[t * top + c] : t * top + c;
-            acc = fmaf(wts[t * top + c], to_f32<TY>(y[row * d + i]), acc);
+            acc = fmaf(wts ? wts[t * top + c] : 1.0f, to_f32<TY>(y[row * d + i]), acc);      // no weights: the plain sum
         }
         out[t * d + i] = from_f32<TO>(acc);
     }

@@ -250,3 +250,33 @@ def paged_latent_attention(q, pages, cache, out, ctx, num_heads: int, wide: int,
         return out
     return ops.attention_sink_generic(q, pages, pages, out, ctx.positions, ctx.token_req, cache.block_table, cache.page_size, num_heads,
                                       1, wide, rank, window, scale, False, value_heads=1, value_row=wide)
+
+
+TALKING_TARGET_CTAS = 2 * 148    # blocks wanted by a step of few tokens: a token's keys are shared out until the GPU is full
+TALKING_MAX_SPLITS = 32
+
+
+def talking_splits(n_tokens: int, window: int, max_kv_len: int, dtype) -> int:
+    """Blocks per token of the fp32-arithmetic kernel with mixed heads.  A float32 run never splits: the order of its sums
+    then depends on the token's position only, whatever else is in the step."""
+    if dtype == torch.float32 or n_tokens >= TALKING_TARGET_CTAS // 2:
+        return 1
+    keys = min(window, max_kv_len) if window > 0 else max_kv_len
+    return max(1, min(-(-TALKING_TARGET_CTAS // n_tokens), -(-keys // 128), TALKING_MAX_SPLITS))
+
+
+def paged_talking_attention(q, cache, out, ctx, num_heads: int, num_kv_heads: int, key_dim: int, value_dim: int, window: int,
+                            scale: float, talk, sink) -> torch.Tensor:
+    """Attention whose scaled scores are mixed between the heads before the softmax (``talk`` [H, H] or None), with a
+    learned sink per head (or None), over pools of keys ``[pages, G, page, key_dim]`` and values ``[pages, G, page, value_dim]``."""
+    n = q.shape[0]
+    splits = talking_splits(n, window, ctx.max_kv_len, q.dtype)
+    scratch = None
+    if splits > 1:
+        skey = ("talking_attention_scratch", n, num_heads, splits, value_dim)
+        if skey not in ctx.plans:
+            ctx.plans[skey] = (torch.empty((n, num_heads, splits, value_dim), dtype=torch.float32, device=q.device),
+                               torch.empty((n, num_heads, splits, 2), dtype=torch.float32, device=q.device))
+        scratch = ctx.plans[skey]
+    return ops.attention_talking(q, cache.arrays["k"], cache.arrays["v"], out, ctx.positions, ctx.token_req, cache.block_table, cache.page_size,
+                                 num_heads, num_kv_heads, key_dim, value_dim, window, scale, talk, sink, splits=splits, scratch=scratch)

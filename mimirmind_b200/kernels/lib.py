@@ -84,6 +84,16 @@ _PROTOTYPES = {
     "mm_latent_prep": [P, I, I, I, P, I, F, P, I, P, P, P, I, P, I, I, I, I, I, I, P],
     "mm_head_matmul": [P, c_longlong, I, P, P, c_longlong, I, I, I, I, I, I, P],
     "mm_head_finish": [P, I, I, F, I, F, F, P, I, P, I, I, I, I, I, P],
+    "mm_moe_router_scored": [P, I, I, P, I, I, I, I, I, I, I, P, P, P],
+    "mm_moe_gemm_act": [P, I, I, P, I, P, I, I, P, P, I, I, I, I, I, I, I, I, I, F, P, P],
+    "mm_talking_prep": [P, I, I, I, I, P, P, F, P, I, I, P, P, P, I, P, I, I, I, I, I, I, P],
+    "mm_attention_talking": [P, P, P, P, I, P, P, I, P, P, P, I, I, I, I, I, I, I, I, F, P, P, P],
+    "mm_forget_gate_prep": [P, I, I, I, I, I, I, P, P, P],
+    "mm_forget_gate_walk": [P, P, P, I, I, I, P, P, c_longlong, P, P, P, I, I, I, I, P],
+    "mm_post_norm": [P, P, P, I, P, P, I, I, I, F, F, F, F, P],
+    "mm_glu_rows": [P, I, c_longlong, P, I, I, I, I, F, P, P],
+    "mm_cast_rows": [P, P, I, c_longlong, P],
+    "mm_scaled_sum2": [P, P, P, I, c_longlong, F, F, P],
     "mm_gemm_tcgen05_grouped": [P, P, P, I, I, I, I, I, I, I, P, P, I, P, P],
 }
 

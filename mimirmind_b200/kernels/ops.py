@@ -1088,9 +1088,13 @@ def moe_route(logits: torch.Tensor, top: int, groups: int, keep: int):
     return idx, wts
 
 
-def moe_router(x: torch.Tensor, w: torch.Tensor, top: int, groups: int, keep: int):
+ROUTER_SCORINGS = {"softmax": 0, "sigmoid": 1}
+
+
+def moe_router(x: torch.Tensor, w: torch.Tensor, top: int, groups: int, keep: int, scoring: str = "softmax"):
     """The router's product (fp32 sums over ``x`` [n, D] and the fp32 matrix ``w`` [E, D]) and its choice in one launch:
-    (experts int32 [n, top], weights fp32 [n, top])."""
+    (experts int32 [n, top], weights fp32 [n, top]).  ``scoring``: ``softmax`` (the chosen scores divided by their sum) or
+    ``sigmoid`` (the chosen scores as they are)."""
     _need(x, "router rows")
     _need(w, "router matrix", torch.float32)
     n, D = x.shape
@@ -1099,8 +1103,8 @@ def moe_router(x: torch.Tensor, w: torch.Tensor, top: int, groups: int, keep: in
         raise KernelError("moe router: shape mismatch")
     idx = torch.empty((n, top), dtype=torch.int32, device=x.device)
     wts = torch.empty((n, top), dtype=torch.float32, device=x.device)
-    check(_lib.load().mm_moe_router(x.data_ptr(), dtype_code(x.dtype), D, w.data_ptr(), n, D, E, int(top), int(groups), int(keep), idx.data_ptr(),
-                                    wts.data_ptr(), _stream()), "moe_router")
+    check(_lib.load().mm_moe_router_scored(x.data_ptr(), dtype_code(x.dtype), D, w.data_ptr(), n, D, E, int(top), int(groups), int(keep),
+                                           ROUTER_SCORINGS[scoring], idx.data_ptr(), wts.data_ptr(), _stream()), "moe_router")
     return idx, wts
 
 
@@ -1140,22 +1144,33 @@ def moe_sort(idx: torch.Tensor, experts: int, with_tiles: bool = False) -> Exper
     return out
 
 
+GLU_ACTIVATIONS = {"silu": 0, "clamped": 1}
+
+
 def moe_gemm(a: torch.Tensor, w: torch.Tensor, rows: ExpertRows, n_rows: int, top: int, gated: bool,
-             out_dtype: torch.dtype, tensor_cores: bool = True, interleaved: bool = False) -> torch.Tensor:
+             out_dtype: torch.dtype, tensor_cores: bool = True, interleaved: bool = False, activation: str = "silu", limit: float = 0.0,
+             row_scale: Optional[torch.Tensor] = None) -> torch.Tensor:
     """The experts' products over their rows.  ``gated``: ``a`` [tokens, K] are the step's rows, ``w`` [E, 2F, K] the gate's
     rows then the up rows of every expert (``interleaved``: alternating in blocks of 8), result ``silu(gate) * up``
     [n_rows, F] in sorted order.  Otherwise ``a`` [n_rows, K] are sorted rows, ``w`` [E, N, K], and row ``order[i]`` of the
-    result [n_rows, N] gets sorted row i's product."""
+    result [n_rows, N] gets sorted row i's product.  A gated product may take another ``activation`` (``clamped``:
+    ``g = min(g, limit)``, ``u = clamp(u, -limit, limit)``, ``g sigmoid(1.702 g) (u + 1)``) and a ``row_scale`` fp32 [tokens, top]
+    that multiplies both halves of a (token, choice) row before it (a weight on the expert's input)."""
     _need(a, "moe rows")
+    if row_scale is not None:
+        _need(row_scale, "moe row scale", torch.float32)
+        if row_scale.numel() != n_rows:
+            raise KernelError("moe gemm: one scale per (token, choice) row is needed")
     _need(w, "moe weights", a.dtype)
     E, rows_w, K = w.shape
     N = rows_w // 2 if gated else rows_w
     if a.shape[1] != K or (not gated and a.shape[0] != n_rows):
         raise KernelError("moe gemm: shape mismatch")
     out = torch.empty((n_rows, N), dtype=out_dtype, device=a.device)
-    check(_lib.load().mm_moe_gemm(a.data_ptr(), dtype_code(a.dtype), a.stride(0), w.data_ptr(), dtype_code(w.dtype), out.data_ptr(),
-                                  dtype_code(out_dtype), N, rows.offsets.data_ptr(), rows.order.data_ptr(), int(n_rows), E, int(top), N, K,
-                                  int(bool(gated)), int(bool(tensor_cores)), int(bool(interleaved)), _stream()), "moe_gemm")
+    check(_lib.load().mm_moe_gemm_act(a.data_ptr(), dtype_code(a.dtype), a.stride(0), w.data_ptr(), dtype_code(w.dtype), out.data_ptr(),
+                                      dtype_code(out_dtype), N, rows.offsets.data_ptr(), rows.order.data_ptr(), int(n_rows), E, int(top), N, K,
+                                      int(bool(gated)), int(bool(tensor_cores)), int(bool(interleaved)), GLU_ACTIVATIONS[activation],
+                                      float(limit), _ptr(row_scale), _stream()), "moe_gemm")
     return out
 
 
@@ -1176,17 +1191,23 @@ def moe_gemm_grouped(a: torch.Tensor, w: torch.Tensor, rows: ExpertRows, swiglu:
     return out
 
 
-def moe_combine(y: torch.Tensor, wts: torch.Tensor, out_dtype: torch.dtype, place: Optional[torch.Tensor] = None) -> torch.Tensor:
+def moe_combine(y: torch.Tensor, wts: Optional[torch.Tensor], out_dtype: torch.dtype, place: Optional[torch.Tensor] = None,
+                top: Optional[int] = None) -> torch.Tensor:
     """``out[t] = sum_c wts[t, c] * y[row(t, c)]`` in the order of the choice; ``row(t, c) = t * top + c``, or
-    ``place[t * top + c]`` when ``y`` stands in sorted order."""
+    ``place[t * top + c]`` when ``y`` stands in sorted order.  ``wts`` None (then ``top`` says how many rows a token has):
+    the plain sum."""
     _need(y, "moe outputs")
-    _need(wts, "moe weights", torch.float32)
-    n, top = wts.shape
+    if wts is not None:
+        _need(wts, "moe weights", torch.float32)
+        n, top = wts.shape
+    else:
+        top = int(top)
+        n = y.shape[0] // top
     d = y.shape[1]
     if y.shape[0] != n * top:
         raise KernelError("moe combine: shape mismatch")
     out = torch.empty((n, d), dtype=out_dtype, device=y.device)
-    check(_lib.load().mm_moe_combine(y.data_ptr(), dtype_code(y.dtype), wts.data_ptr(), _ptr(place), out.data_ptr(), dtype_code(out_dtype), n, top, d,
+    check(_lib.load().mm_moe_combine(y.data_ptr(), dtype_code(y.dtype), _ptr(wts), _ptr(place), out.data_ptr(), dtype_code(out_dtype), n, top, d,
                                      _stream()), "moe_combine")
     return out
 
@@ -1368,4 +1389,182 @@ def head_finish(att: torch.Tensor, heads: int, value_dim: int, *, pair: bool = F
                                      _ptr(gate), gate.stride(0) if gate is not None else 0, out.data_ptr(), dtype_code(att.dtype),
                                      dtype_code(out_dtype), n, int(heads),
                                      int(value_dim), _stream()), "head_finish")
+    return out
+
+
+# ---- attention with mixed heads (csrc/attention_talking.cu) -----------------------------------------------------------------
+def talking_prep(rows: torch.Tensor, q_off: int, k_off: int, v_off: int, q_norm: Optional[torch.Tensor], k_norm: Optional[torch.Tensor],
+                 eps: float, rot: Optional[torch.Tensor], rot_dims: int, v_unit: bool, q_out: torch.Tensor, k_pages: Optional[torch.Tensor],
+                 v_pages: Optional[torch.Tensor], slots: Optional[torch.Tensor], page_size: int, heads: int, kv_heads: int, key_dim: int,
+                 value_dim: int) -> None:
+    """Between the projections (and convolutions) of an attention and its kernel: from fp32 rows [n, ld] every q head
+    (``heads * key_dim`` numbers at ``q_off``) and k head (``kv_heads * key_dim`` at ``k_off``) is RMS-normed over its
+    ``key_dim`` numbers with the fp32 weight ``q_norm`` / ``k_norm`` (None: not normed) and its first ``rot_dims`` numbers
+    are turned by ``rot`` [n, rot_dims/2, 2] (number i pairs with i + rot_dims/2); every v head (``kv_heads * value_dim``
+    at ``v_off``) is divided by its root mean square when ``v_unit``.  q goes to ``q_out`` [n, heads * key_dim], k and v
+    into their pages ``[pages, kv_heads, page_size, size]`` at ``slots``."""
+    if rows.dtype != torch.float32 or not rows.is_cuda or rows.stride(1) != 1:
+        raise KernelError("attention prep: fp32 rows with unit column stride are needed")
+    n = rows.shape[0]
+    _need(q_out, "q_out")
+    if q_out.shape != (n, heads * key_dim):
+        raise KernelError("attention prep: q_out has another shape")
+    for w, what in ((q_norm, "q norm"), (k_norm, "k norm")):
+        if w is not None:
+            _need(w, what, torch.float32)
+            if w.numel() != key_dim:
+                raise KernelError(f"attention prep: the {what} weight has one number per key channel")
+    if rot_dims:
+        _need(rot, "rotation table", torch.float32)
+        if rot.shape != (n, rot_dims // 2, 2):
+            raise KernelError("attention prep: rotation table of another shape")
+    if max(q_off + heads * key_dim, k_off + kv_heads * key_dim, v_off + kv_heads * value_dim) > rows.shape[1]:
+        raise KernelError("attention prep: columns outside the row")
+    if k_pages is not None:
+        _need(k_pages, "k_pages", q_out.dtype)
+        _need(v_pages, "v_pages", q_out.dtype)
+        _need(slots, "slots", torch.int32)
+        if k_pages.shape[1:] != (kv_heads, page_size, key_dim) or v_pages.shape[1:] != (kv_heads, page_size, value_dim):
+            raise KernelError("attention prep: page pool shape mismatch")
+    check(_lib.load().mm_talking_prep(rows.data_ptr(), rows.stride(0), int(q_off), int(k_off), int(v_off), _ptr(q_norm), _ptr(k_norm), float(eps),
+                                      _ptr(rot) if rot_dims else None, int(rot_dims), int(bool(v_unit)), q_out.data_ptr(), _ptr(k_pages),
+                                      _ptr(v_pages), dtype_code(q_out.dtype), _ptr(slots) if k_pages is not None else None, int(page_size), n,
+                                      int(heads), int(kv_heads), int(key_dim), int(value_dim), _stream()), "talking_prep")
+
+
+def attention_talking(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, out: torch.Tensor, positions: torch.Tensor,
+                      token_req: torch.Tensor, block_table: torch.Tensor, page_size: int, num_heads: int, num_kv_heads: int, key_dim: int,
+                      value_dim: int, window: int, scale: float, talk: Optional[torch.Tensor], sink: Optional[torch.Tensor],
+                      splits: int = 1, scratch=None) -> torch.Tensor:
+    """Causal (or windowed) attention whose scaled scores are mixed between the heads before the softmax,
+    ``s_h = sum_g talk[h, g] r_g`` (``talk`` fp32 [H, H]; None: not mixed), with ``exp(sink_h)`` in head h's denominator
+    (``sink`` fp32 [H]; None: plain softmax); fp32 arithmetic, any sizes.  ``splits`` > 1 shares a token's keys out over
+    that many blocks (``scratch``: fp32 [n, H, splits, dv] and [n, H, splits, 2]) and merges them in a second launch."""
+    _need(q, "q")
+    _need(k_pages, "k_pages", q.dtype)
+    _need(v_pages, "v_pages", q.dtype)
+    _need(out, "attention out", q.dtype)
+    _need(positions, "positions", torch.int32)
+    _need(token_req, "token_req", torch.int32)
+    _need(block_table, "block_table", torch.int32)
+    n = q.shape[0]
+    if q.shape != (n, num_heads * key_dim) or out.shape != (n, num_heads * value_dim):
+        raise KernelError("attention: q or out has another shape")
+    if k_pages.shape[1:] != (num_kv_heads, page_size, key_dim) or v_pages.shape[1:] != (num_kv_heads, page_size, value_dim):
+        raise KernelError("attention: page pool shape mismatch")
+    for t, what, count in ((talk, "head mixing matrix", num_heads * num_heads), (sink, "sink logits", num_heads)):
+        if t is not None:
+            _need(t, what, torch.float32)
+            if t.numel() != count:
+                raise KernelError(f"attention: the {what} has another size")
+    part_o = part_ml = None
+    if splits > 1:
+        part_o, part_ml = scratch if scratch is not None else (
+            torch.empty((n, num_heads, splits, value_dim), dtype=torch.float32, device=q.device),
+            torch.empty((n, num_heads, splits, 2), dtype=torch.float32, device=q.device))
+    check(_lib.load().mm_attention_talking(q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), out.data_ptr(), dtype_code(q.dtype), _ptr(part_o),
+                                           _ptr(part_ml), int(splits), positions.data_ptr(), token_req.data_ptr(), block_table.data_ptr(),
+                                           block_table.shape[1], int(page_size), n, int(num_heads), int(num_kv_heads), int(key_dim), int(value_dim),
+                                           int(window), float(scale), _ptr(talk), _ptr(sink), _stream()), "attention_talking")
+    return out
+
+
+# ---- a forget gate per key channel (csrc/linear_state.cu) -----------------------------------------------------------------------
+def forget_gate_prep(x: torch.Tensor, q_off: int, f_off: int, n_qf: int, bias: Optional[torch.Tensor], lower: Optional[torch.Tensor],
+                     silu_q: bool = True) -> None:
+    """In place on the fp32 rows ``x`` [n, ld]: silu on the ``n_qf`` numbers at ``q_off``; the ``n_qf`` numbers ``z`` at
+    ``f_off`` become the forget gate ``l + (1 - l) sigmoid(z + bias)`` with the lower bound ``l`` per channel (both fp32
+    [n_qf] or None)."""
+    _need(x, "projection rows", torch.float32)
+    for t, what in ((bias, "forget bias"), (lower, "lower bound")):
+        if t is not None:
+            _need(t, what, torch.float32)
+            if t.numel() != n_qf:
+                raise KernelError(f"forget gate: the {what} has one number per channel")
+    check(_lib.load().mm_forget_gate_prep(x.data_ptr(), x.shape[1], x.shape[0], int(q_off), int(f_off), int(n_qf), int(bool(silu_q)), _ptr(bias),
+                                          _ptr(lower), _stream()), "forget_gate_prep")
+
+
+def forget_gate_walk(q: torch.Tensor, f: torch.Tensor, v: torch.Tensor, state: torch.Tensor, req_meta: Optional[torch.Tensor],
+                     slots: torch.Tensor, positions: torch.Tensor, n_requests: int, heads: int, dk: int, dv: int) -> torch.Tensor:
+    """Per head ``S <- diag(f) S + (1 - f) v^T; o = S^T q`` over each request's tokens in order.  q, f: fp32 column slices
+    [n, heads * dk], v [n, heads * dv] (any row stride); ``state`` [slots, stride] fp32 holds S as [heads, dv, dk] at its
+    start and is left updated.  Returns o fp32 [n, heads * dv]."""
+    for t, what in ((q, "q"), (f, "f"), (v, "v")):
+        if t.dtype != torch.float32 or not t.is_cuda or t.stride(1) != 1:
+            raise KernelError(f"forget gate walk {what}: fp32 rows with unit column stride are needed")
+    n = q.shape[0]
+    if q.shape[1] != heads * dk or f.shape != q.shape or v.shape != (n, heads * dv):
+        raise KernelError("forget gate walk: shape mismatch")
+    if state.dtype != torch.float32 or state.stride(-1) != 1 or state.shape[1] < heads * dv * dk:
+        raise KernelError("forget gate walk: the state is fp32 [slots, >= heads * dv * dk]")
+    _need(slots, "state slots", torch.int32)
+    _need(positions, "positions", torch.int32)
+    out = torch.empty((n, heads * dv), dtype=torch.float32, device=q.device)
+    check(_lib.load().mm_forget_gate_walk(q.data_ptr(), f.data_ptr(), v.data_ptr(), q.stride(0), f.stride(0), v.stride(0), out.data_ptr(),
+                                          state.data_ptr(), state.stride(0), _ptr(req_meta), slots.data_ptr(), positions.data_ptr(),
+                                          int(n_requests), int(heads), int(dk), int(dv), _stream()), "forget_gate_walk")
+    return out
+
+
+# ---- the norm after the sum, gated activations as a pass of their own (csrc/post_norm.cu) ------------------------------------------
+def post_norm(residual: torch.Tensor, a: Optional[torch.Tensor], b: Optional[torch.Tensor], weight: torch.Tensor, eps: float, alpha: float,
+              ca: float = 1.0, cb: float = 1.0, out: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+    """``y = alpha x + ca a + cb b``, ``x <- y / sqrt(mean(y^2) + eps) * weight`` on the fp32 residual ``x`` [n, D] in place;
+    a, b: branch outputs [n, D] of one dtype (either may be None); ``out`` also gets the new rows in its own dtype."""
+    _need(residual, "residual", torch.float32)
+    _need(weight, "norm weight", torch.float32)
+    n, D = residual.shape
+    dt = None
+    for t in (a, b):
+        if t is not None:
+            _need(t, "branch", dt)
+            dt = t.dtype
+            if t.shape != (n, D):
+                raise KernelError("post norm: a branch has another shape")
+    if out is not None:
+        _need(out, "post norm out")
+        if out.shape != (n, D):
+            raise KernelError("post norm: out has another shape")
+    if a is None and b is not None:
+        a, ca, b = b, cb, None
+    b_dtype = dtype_code(dt) if dt is not None else F32                  # no branch: the kernel reads none
+    out_dtype = dtype_code(out.dtype) if out is not None else b_dtype    # no out: the kernel writes none
+    check(_lib.load().mm_post_norm(residual.data_ptr(), _ptr(a), _ptr(b), b_dtype, weight.data_ptr(), _ptr(out), out_dtype, n, D, float(alpha),
+                                   float(ca), float(cb), float(eps), _stream()), "post_norm")
+    return out
+
+
+def glu_rows(gate_up: torch.Tensor, out_dtype: torch.dtype, activation: str = "silu", limit: float = 0.0,
+             row_scale: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The gated activation of rows [n, 2F] whose first F columns are the gate's and the rest the up projection's
+    (``GLU_ACTIVATIONS``), each row multiplied by ``row_scale`` [n] first when given: [n, F] of ``out_dtype``."""
+    if not gate_up.is_cuda or gate_up.stride(1) != 1 or gate_up.shape[1] % 2:
+        raise KernelError("gated activation: rows of an even width with unit column stride are needed")
+    n, F2 = gate_up.shape
+    if row_scale is not None:
+        _need(row_scale, "row scale", torch.float32)
+    out = torch.empty((n, F2 // 2), dtype=out_dtype, device=gate_up.device)
+    check(_lib.load().mm_glu_rows(gate_up.data_ptr(), dtype_code(gate_up.dtype), gate_up.stride(0), out.data_ptr(), dtype_code(out_dtype), n, F2 // 2,
+                                  GLU_ACTIVATIONS[activation], float(limit), _ptr(row_scale), _stream()), "glu_rows")
+    return out
+
+
+def cast_rows(x: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+    """fp32 rows in ``out_dtype``."""
+    _need(x, "rows", torch.float32)
+    out = torch.empty(x.shape, dtype=out_dtype, device=x.device)
+    check(_lib.load().mm_cast_rows(x.data_ptr(), out.data_ptr(), dtype_code(out_dtype), x.numel(), _stream()), "cast_rows")
+    return out
+
+
+def scaled_sum2(a: torch.Tensor, b: torch.Tensor, ca: float, cb: float) -> torch.Tensor:
+    """``ca * a + cb * b`` element by element."""
+    _need(a, "scaled sum a")
+    _need(b, "scaled sum b", a.dtype)
+    if a.shape != b.shape:
+        raise KernelError("scaled sum: shape mismatch")
+    out = torch.empty_like(a)
+    check(_lib.load().mm_scaled_sum2(a.data_ptr(), b.data_ptr(), out.data_ptr(), dtype_code(a.dtype), a.numel(), float(ca), float(cb), _stream()),
+          "scaled_sum2")
     return out

@@ -204,6 +204,69 @@ class StreamConnectionsBlock(Block):
         return NormedRows(made) if made is not None else None
 
 
+@BLOCKS.register("post_norm")
+class PostNormBlock(Block):
+    """The norm after the sum: ``x <- norm1(alpha x + mixer(x))``, then ``x <- norm2(alpha x + ffn(x))``; the sublayers read the
+    stream itself, and a layer whose feed-forward is of kind ``none`` has the first sublayer only.  Both norms are of the kind
+    ``y w / sqrt(mean(y^2) + eps)`` (``Norm.factors``).
+
+    The scaling of the stream, the sum and the norm are one launch that leaves the fp32 stream and its rounding to the
+    activation dtype, which is what the next sublayer's products read.  A mixer or feed-forward whose result is a weighted
+    sum of two branches (``forward_branches``) hands the branches over and the same launch adds them.  The block that follows,
+    if it is of this kind, gets the rounded stream as ``NormedRows``.
+
+    spec params: alpha."""
+
+    def __init__(self, *args, **kwargs):
+        super().__init__(*args, **kwargs)
+        from .mlp import NoFeedForward
+        self.alpha = float(self.spec.get("alpha", 1.0))
+        self.has_ffn = not isinstance(self.feed_forward, NoFeedForward)
+        self.norms = []
+        for norm in (self.mixer_norm,) + ((self.ffn_norm,) if self.has_ffn else ()):
+            f = norm.factors()
+            if f is None:
+                raise ValueError("post_norm block: its norms must be of the kind y * w / sqrt(mean(y^2) + eps)")
+            self.norms.append((f[0].float().contiguous(), float(f[1])))
+
+    @staticmethod
+    def _branches(part, *args):
+        many = part.forward_branches(*args) if hasattr(part, "forward_branches") else None
+        if many is None:
+            return [(part.forward(*args), 1.0)]
+        if len(many) > 2:
+            raise ValueError("post_norm block: a sublayer hands over at most two branches")
+        return many
+
+    def _sublayer(self, residual: torch.Tensor, branches, which: int):
+        from ..kernels import ops
+        w, eps = self.norms[which]
+        (a, ca), (b, cb) = branches[0], (branches[1] if len(branches) > 1 else (None, 1.0))
+        if self.rt.dtype == torch.float32:
+            ops.post_norm(residual, a, b, w, eps, self.alpha, ca, cb)
+            return residual                          # a float32 run reads the stream itself
+        out = torch.empty(residual.shape, dtype=self.rt.dtype, device=residual.device)
+        return ops.post_norm(residual, a, b, w, eps, self.alpha, ca, cb, out=out)
+
+    def forward(self, residual: torch.Tensor, pending, ctx: StepContext, cache: LayerCache,
+                successor: Optional[Block] = None):
+        from ..kernels import ops
+        dump = ctx.dump or (lambda stage, t: None)
+        if isinstance(pending, NormedRows):
+            h = pending.x
+        else:
+            if pending is not None:
+                ops.add_residual(residual, pending)
+            h = residual if self.rt.dtype == torch.float32 else ops.cast_rows(residual, self.rt.dtype)
+        dump("attn_norm", h)
+        h = self._sublayer(residual, self._branches(self.mixer, h, ctx, cache), 0)
+        if self.has_ffn:
+            h = self._sublayer(residual, self._branches(self.feed_forward, h, ctx), 1)
+        if ctx.dump is not None:
+            dump("l_out", residual)
+        return NormedRows(h) if isinstance(successor, PostNormBlock) else None
+
+
 def ops_add(residual: torch.Tensor, delta: torch.Tensor) -> None:
     from ..kernels import ops
     ops.add_residual(residual, delta)

@@ -8,7 +8,11 @@ engine's state slots::
 One class covers the family; what differs between its members is a parameter:
 
 * ``decay``: a list with one constant per head (retention, lightning attention), or the name stem of a learned decay per
-  token, ``g = exp(-exp(A_log) softplus(W_a h + dt_bias))`` (gated delta rule);
+  token, ``g = exp(-exp(A_log) softplus(W_a h + dt_bias))`` (gated delta rule), or ``"forget_gate"`` (HGRN2): the decay is a
+  vector over the key channels whose complement is the write strength, ``f = l + (1 - l) sigmoid(W_k h + f_bias)`` with a lower
+  bound ``l`` per channel (``lower``), ``S <- diag(f) S + (1 - f) v^T``: the ``k`` projection is the gate's, there is no key
+  of its own, q and k have as many heads as v, and of the activation only q's part applies;
+* ``g``: the name of the output gate's projection, or None for no gate;
 * ``delta``: the name of the projection of the write strength ``beta = sigmoid(W_b h)``, or None for the plain update;
 * ``conv``: taps of a short causal convolution per channel on q, k and v before the activation (its last inputs are
   state too), or 0;
@@ -54,8 +58,11 @@ class LinearStateMixer(Mixer):
     def tensor_specs(cls, spec: PartSpec, prefix: str) -> List[TensorSpec]:
         d, H, G, dk, dv = spec["hidden"], spec["heads"], spec["qk_heads"], spec["key_dim"], spec["value_dim"]
         out = [TensorSpec(prefix + spec["q"], (G * dk, d)), TensorSpec(prefix + spec["k"], (G * dk, d)),
-               TensorSpec(prefix + spec["v"], (H * dv, d)), TensorSpec(prefix + spec["g"], (H * dv, d)),
-               TensorSpec(prefix + spec["o"], (d, H * dv))]
+               TensorSpec(prefix + spec["v"], (H * dv, d)), TensorSpec(prefix + spec["o"], (d, H * dv))]
+        if spec.get("g"):
+            out.append(TensorSpec(prefix + spec["g"], (H * dv, d)))
+        if spec["decay"] == "forget_gate":
+            out += [TensorSpec(prefix + spec["f_bias"], (G * dk,), role="bias"), TensorSpec(prefix + spec["lower"], (G * dk,), role="lower_bound")]
         taps = int(spec.get("conv", 0) or 0)
         if taps:
             sfx = spec.get("conv_suffix", ".conv")
@@ -63,7 +70,7 @@ class LinearStateMixer(Mixer):
                     TensorSpec(prefix + spec["v"] + sfx, (H * dv, taps), role="taps")]
         if spec.get("delta"):
             out.append(TensorSpec(prefix + spec["delta"], (H, d)))
-        if not isinstance(spec["decay"], (list, tuple)):
+        if not isinstance(spec["decay"], (list, tuple)) and spec["decay"] != "forget_gate":
             out += [TensorSpec(prefix + spec["a"], (H, d)), TensorSpec(prefix + spec["A_log"], (H,), role="bias"),
                     TensorSpec(prefix + spec["dt_bias"], (H,), role="bias")]
         if spec.get("out_weight"):
@@ -85,9 +92,14 @@ class LinearStateMixer(Mixer):
         self.activation = spec.get("activation")
         if self.activation not in (None, "silu"):
             raise ValueError("linear state: the activation is 'silu' or None")
-        self.learned_decay = not isinstance(spec["decay"], (list, tuple))
+        self.forget_gate = spec["decay"] == "forget_gate"
+        self.learned_decay = not isinstance(spec["decay"], (list, tuple)) and not self.forget_gate
         self.delta = bool(spec.get("delta"))
-        names = ["q", "k", "v"] + (["delta"] if self.delta else []) + (["a"] if self.learned_decay else []) + ["g"]
+        self.has_gate = bool(spec.get("g"))
+        if self.forget_gate and (G != H or self.delta or spec.get("conv") or spec.get("rotary") or spec.get("unit_eps") is not None):
+            raise ValueError("linear state: a forget gate per channel goes with as many q/k heads as heads, and without the delta rule, "
+                             "convolution, rotation or unit length")
+        names = ["q", "k", "v"] + (["delta"] if self.delta else []) + (["a"] if self.learned_decay else []) + (["g"] if self.has_gate else [])
         ws = [weights.take(spec[n]) for n in names]
         if len({w.dtype for w in ws}) > 1:
             ws = [w.float() for w in ws]
@@ -106,8 +118,11 @@ class LinearStateMixer(Mixer):
         if self.taps:
             sfx = spec.get("conv_suffix", ".conv")
             self.conv_taps = torch.cat([weights.take(spec[n] + sfx).float() for n in ("q", "k", "v")], dim=0).contiguous()
-        self.head_decay = self.A_log = self.dt_bias = None
-        if self.learned_decay:
+        self.head_decay = self.A_log = self.dt_bias = self.f_bias = self.lower = None
+        if self.forget_gate:
+            self.f_bias = weights.take(spec["f_bias"]).float().contiguous()
+            self.lower = weights.take(spec["lower"]).float().contiguous()
+        elif self.learned_decay:
             self.A_log = weights.take(spec["A_log"]).float().contiguous()
             self.dt_bias = weights.take(spec["dt_bias"]).float().contiguous()
         else:
@@ -143,6 +158,13 @@ class LinearStateMixer(Mixer):
         H, G, dk, dv = self.heads, self.qk_heads, self.dk, self.dv
         a = linear(x, self.w_in, None, self.rt, out_dtype=torch.float32)
         state = cache.state
+        if self.forget_gate:
+            # the walk is strictly token by token: one order of operations whatever the cutting, in either number format
+            ops.forget_gate_prep(a, self.q_off, self.k_off, H * dk, self.f_bias, self.lower, silu_q=self.activation == "silu")
+            o = ops.forget_gate_walk(a[:, self.q_off:self.q_off + H * dk], a[:, self.k_off:self.k_off + H * dk],
+                                     a[:, self.v_off:self.v_off + H * dv], state, ctx.req_meta, ctx.state_slots, ctx.positions,
+                                     ctx.n_requests, H, dk, dv)
+            return self._finish(o, a)
         qkv, gate_rows = a, None          # where q, k and v stand, and (if elsewhere) the rows with the gates' columns
         if self.taps and ctx.max_q_len >= CONV_BY_TOKEN_FROM:
             qkv, gate_rows = ops.causal_conv_tokens(a, self.channels, self.conv_taps, state[:, self.state_size:], ctx.token_req, ctx.req_meta,
@@ -170,7 +192,12 @@ class LinearStateMixer(Mixer):
         else:
             o = ops.linear_state_walk(qs, ks_, vs, state, ctx.req_meta, ctx.state_slots, ctx.positions, ctx.n_requests, H, G, dk, dv,
                                       gate=gate, beta=beta, head_decay=self.head_decay)
-        g = a[:, self.g_off:self.g_off + H * dv]
+        return self._finish(o, a)
+
+    def _finish(self, o: torch.Tensor, a: torch.Tensor) -> torch.Tensor:
+        """The norm behind the heads, the output gate (its columns stand in the projection's rows ``a``) and the output projection."""
+        H, dv = self.heads, self.dv
+        g = a[:, self.g_off:self.g_off + H * dv] if self.has_gate else None
         if self.out_norm == "head":
             y = ops.gated_group_norm(o, H, dv, self.rt.dtype, eps=self.eps, weight=self.out_weight, gate=g, activation=self.gate_activation)
         else:

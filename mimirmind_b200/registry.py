@@ -118,4 +118,4 @@ def _ensure_builtin() -> None:
         return
     _builtin_loaded = True
     from . import parts  # noqa: F401  (registers part kinds)
-    from .models import bigerax, domelix, qwen2, tupunex  # noqa: F401  (register the architectures)
+    from .models import bigerax, domelix, qwen2, tupunex, zubarax  # noqa: F401  (register the architectures)

@@ -145,6 +145,10 @@ def random_tensors(spec: ModelSpec, seed: int, dtype: torch.dtype, device="cpu")
             x = torch.eye(ts.shape[0], device=device) + 0.05 * x
         elif ts.role == "mix":
             x = (0.5 + MIX_STD * x).clamp(0.05, 0.95)
+        elif ts.role == "lower_bound":    # the floor of a forget gate: inside (0, 1)
+            x = torch.sigmoid(x)
+        elif ts.role == "head_mix":       # how the heads' scores are mixed: near the identity
+            x = torch.eye(ts.shape[0], device=device) + 0.3 * x
         else:
             x = MATRIX_STD * x
         out[name] = x.to(dtype)
