@@ -260,6 +260,7 @@ class PostNormBlock(Block):
             h = residual if self.rt.dtype == torch.float32 else ops.cast_rows(residual, self.rt.dtype)
         dump("attn_norm", h)
         h = self._sublayer(residual, self._branches(self.mixer, h, ctx, cache), 0)
+        dump("attn_out", residual)               # the stream behind the mixer's sublayer
         if self.has_ffn:
             h = self._sublayer(residual, self._branches(self.feed_forward, h, ctx), 1)
         if ctx.dump is not None:

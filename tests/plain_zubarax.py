@@ -187,7 +187,7 @@ def experts_feed_forward(h, w, prefix, f):
 # ---- the model ----------------------------------------------------------------------------------------------------
 def forward(cfg, w, tokens, positions=None, collect: Optional[List[np.ndarray]] = None):
     """Logits [T, vocab] of one sequence; ``collect`` receives the stream after every layer run."""
-    eps, alpha = cfg["norm"]["eps"], cfg["postln_alpha"]
+    eps, alpha = cfg["norm"]["eps"], cfg.get("postln_alpha", 1.0)
     T = len(tokens)
     positions = list(range(T)) if positions is None else positions
     x = w["embed"][np.asarray(tokens)] * cfg.get("embedding", {}).get("scale", 1.0)
