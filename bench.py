@@ -166,7 +166,7 @@ def run_workload(name: str, layers: int) -> int:
     return 0 if verified else 1
 
 
-# ---- another design beside the closest existing one, at equal size (--compare bigerax | domelix | tupunex) ---------------------------------------
+# ---- another design beside the closest existing one, at equal size (--compare bigerax | domelix | tupunex | zubarax) ---------------------------------------
 # Layer sizes that resemble a real model's; both models get the same width, heads, key size, window, layer count and
 # vocabulary, and feed-forwards of equal parameter count (two matrices of ff against three of 2/3 ff).
 COMPARE_SIZES = {
@@ -218,6 +218,22 @@ def tupunex_config(z):
             "layers": layers}
 
 
+def zubarax_config(z):
+    """Every layer the two mixers side by side (attention with mixed heads over all earlier tokens, and a forget-gate state of
+    the same head geometry) and routed experts of Domelix's size (16 experts, 4 chosen, weight on the input) plus a shared
+    expert; the second half of the layers runs with the first half's tensors."""
+    d, H, G, dk, dv = z["width"], z["heads"], z["kv_heads"], z["dim"], z["vdim"]
+    expert_ff = -(-(2 * z["ff"] // 12) // 64) * 64
+    mlp = {"kind": "moe", "expert": {"ff": expert_ff, "limit": 7.0}, "router": {"experts": 16, "top": 4}, "shared": {"ff": expert_ff, "limit": 7.0}}
+    par = {"type": "parallel", "mlp": mlp,
+           "mixer": {"left": {"heads": H, "kv_heads": G, "dim": dk, "vdim": dv, "scale": dk ** -0.5, "conv": 4, "rot": {"dims": dk, "base": 10000.0}},
+                     "right": {"heads": H, "dim": dk, "vdim": dv}, "left_scale": 1.0, "right_scale": 1.0}}
+    own = max(1, z["layers"] // 2)
+    layers = [dict(par) if i < own else dict(par, weights_of=i % own) for i in range(z["layers"])]
+    return {"architecture": "Zubarax", "vocab": z["vocab"], "width": d, "norm": {"eps": 1e-6}, "postln_alpha": 2.0, "embedding": {"scale": 1.0},
+            "layers": layers}
+
+
 def qwen2_config(z, context):
     inter = -(-(2 * z["ff"] // 3) // 64) * 64
     return dict(architectures=["Qwen2ForCausalLM"], model_type="qwen2", num_hidden_layers=z["layers"], hidden_size=z["width"],
@@ -228,7 +244,7 @@ def qwen2_config(z, context):
 
 def run_compare(args) -> int:
     """Prefill and decode throughput of one design beside the closest other one at equal size (random weights, bfloat16):
-    Bigerax beside the Qwen2 decoder, Domelix beside Bigerax, Tupunex beside the Qwen2 decoder; one prompt in one step (median of five), and the captured
+    Bigerax beside the Qwen2 decoder, Domelix beside Bigerax, Tupunex beside the Qwen2 decoder, Zubarax beside Domelix; one prompt in one step (median of five), and the captured
     decode step at the given batch over prompts of that length."""
     import numpy as np
     import torch
@@ -244,9 +260,10 @@ def run_compare(args) -> int:
     prompt_len = args.prompt_len or PROMPT_LEN
     steps, warmup, batch = max(1, min(args.steps, 128)), max(3, args.warmup), max(1, args.batch)
     context = -(-(prompt_len + SETTLE_STEPS + warmup + steps + 1) // 1024) * 1024
-    first, second = {"bigerax": ("bigerax", "qwen2"), "domelix": ("domelix", "bigerax"), "tupunex": ("tupunex", "qwen2")}[args.compare]
+    first, second = {"bigerax": ("bigerax", "qwen2"), "domelix": ("domelix", "bigerax"), "tupunex": ("tupunex", "qwen2"),
+                     "zubarax": ("zubarax", "domelix")}[args.compare]
     configs = {"bigerax": lambda z: bigerax_config(z), "qwen2": lambda z: qwen2_config(z, context), "domelix": lambda z: domelix_config(z),
-               "tupunex": lambda z: tupunex_config(z)}
+               "tupunex": lambda z: tupunex_config(z), "zubarax": lambda z: zubarax_config(z)}
     out = {"compare": first, "beside": second, "dtype": "bf16", "data": "synthetic", "prompt_len": prompt_len, "batch": batch,
            "steps": steps, "warmup": warmup, "sizes": {}}
     sizes = [args.size] if args.size else sorted(COMPARE_SIZES)
@@ -366,7 +383,7 @@ def main() -> int:
                     help="with --only decode or prefill: prompts of this many tokens instead of 2,048 (the context grows with them)")
     ap.add_argument("--opt", action="append", default=[], metavar="NAME=VALUE",
                     help="set a tunable of the library's dispatch (csrc/exec/exec.h, Options) for this run, e.g. cluster_max_wanted=64")
-    ap.add_argument("--compare", default="", choices=["", "bigerax", "domelix", "tupunex"],
+    ap.add_argument("--compare", default="", choices=["", "bigerax", "domelix", "tupunex", "zubarax"],
                     help="instead of the default run: prefill and decode throughput of that design beside the closest other one (bigerax "
                          "beside the Qwen2 decoder, domelix beside bigerax, tupunex beside the Qwen2 decoder) at equal size, at layer sizes that resemble a real model's (random weights; --size, --layers, --batch, --prompt-len, --steps)")
     ap.add_argument("--size", default="", choices=[""] + sorted(COMPARE_SIZES), help="with --compare: one size only")

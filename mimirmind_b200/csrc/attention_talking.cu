@@ -13,8 +13,11 @@
 // numbers of every q and k head, values divided by their root mean square per head, and the write of keys and values
 // into their pages; (2) the fp32-arithmetic attention kernel for any sizes, one block per query token (and key split),
 // its keys in chunks of 32 aligned to absolute position so that a token's result depends on its own position and keys
-// only.
+// only; (3) the tensor-core kernel for bfloat16 (mma.sync m16n8k16, fp32 scores): a CTA owns 16 query tokens of one
+// request with all their heads; per key tile the warps share out the heads' raw score products, leave them in shared
+// memory, and every warp then mixes, masks and softmaxes the scores of its own heads and multiplies them with the values.
 #include "common.cuh"
+#include "mma_sync.cuh"
 
 // ---------------------------------------------------------------------------------------------------------------
 // norm per head + rotation + unit values + cache write
@@ -287,5 +290,341 @@ MM_EXPORT int mm_attention_talking(const void* q, const void* k_pages, const voi
     else if (dtype == MM_BF16) TALK_LAUNCH(bf);
     else MM_REQUIRE(false, "attention: dtype must be float32 or bfloat16");
 #undef TALK_LAUNCH
+    return MM_OK;
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// attention with mixed heads on the tensor cores (bfloat16 operands, fp32 scores, mixing, softmax and sums)
+// ---------------------------------------------------------------------------------------------------------------
+// A tile: 16 consecutive tokens (or fewer) of one request, tiles[i] = (first token, tokens); positions and the request are
+// read from the device, so a captured decode step replays the same list.  grid = (tiles, head groups, key splits).
+// A CTA of NW warps: all H heads' raw scores of a key tile are made by the warps in turn (head g by warp g mod NW, at most
+// two per warp) and written, scaled, to shared memory over the key tile they were made from; warp w then owns HPW heads of
+// the CTA's head group: it mixes their scores from all raw heads (fp32), masks, keeps the running maximum and mass per
+// row, and adds P V to its accumulators.  Shared memory: Q [H][16][dk + 8], K [G][TK][dk + 8] (then raw [H][16][TK + 8]
+// fp32 in the same place), V [G][TK][dv + 8], the head group's rows of the mixing matrix.
+#define TALK_LOG2E 1.4426950408889634f
+
+template <int DV, int HPW, int TK>
+__global__ void __launch_bounds__(512) attention_talking_mma_kernel(
+    const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_pages, const __nv_bfloat16* __restrict__ v_pages,
+    __nv_bfloat16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml, const int32_t* __restrict__ tiles,
+    const int32_t* __restrict__ positions, const int32_t* __restrict__ token_req, const int32_t* __restrict__ block_table, int table_width,
+    int page_size, int H, int G, int dk, int Hc, int window, float scale, const float* __restrict__ talk, const float* __restrict__ sink) {
+    constexpr int NT_S = TK / 8, NT_O = DV / 8, RS = TK + 8, VS = DV + 8;
+    extern __shared__ __align__(16) unsigned char tm_smem[];
+    const int KS = dk + 8;
+    __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(tm_smem);
+    const size_t q_bytes = (size_t)H * 16 * KS * 2;
+    const size_t k_bytes = (size_t)G * TK * KS * 2, raw_bytes = (size_t)H * 16 * RS * 4;
+    __nv_bfloat16* sK = reinterpret_cast<__nv_bfloat16*>(tm_smem + q_bytes);
+    float* sRaw = reinterpret_cast<float*>(tm_smem + q_bytes);
+    const size_t kr_bytes = ((k_bytes > raw_bytes ? k_bytes : raw_bytes) + 15) & ~(size_t)15;
+    __nv_bfloat16* sV = reinterpret_cast<__nv_bfloat16*>(tm_smem + q_bytes + kr_bytes);
+    float* sT = reinterpret_cast<float*>(tm_smem + q_bytes + kr_bytes + (size_t)G * TK * VS * 2);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, NW = blockDim.x >> 5, threads = blockDim.x;
+    const int t0 = tiles[2 * blockIdx.x], nq = tiles[2 * blockIdx.x + 1];
+    const int hg = blockIdx.y, split = blockIdx.z, splits = gridDim.z;
+    const int pos0 = positions[t0];
+    const int32_t* table = block_table + (size_t)token_req[t0] * table_width;
+    const int rep = H / G;
+    const int hi_all = pos0 + nq;                                                   // keys below this position
+    const int lo_all = (window > 0 && pos0 + 1 > window) ? pos0 + 1 - window : 0;
+    // key tiles of this split, aligned to TK
+    const int kt_first = lo_all / TK, kt_end = (hi_all + TK - 1) / TK;
+    const int per = (kt_end - kt_first + splits - 1) / splits;
+    const int kt0 = kt_first + split * per, kt1 = min(kt_end, kt0 + per);
+
+    // Q of all heads, rows beyond the tile's tokens zero
+    const int qparts = dk / 8;
+    for (int i = tid; i < H * 16 * qparts; i += threads) {
+        const int part = i % qparts, r = (i / qparts) % 16, h = i / (qparts * 16);
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (r < nq) v = *reinterpret_cast<const uint4*>(q + ((size_t)(t0 + r) * H + h) * dk + part * 8);
+        *reinterpret_cast<uint4*>(sQ + ((size_t)h * 16 + r) * KS + part * 8) = v;
+    }
+    const int h_first = hg * Hc;
+    for (int i = tid; i < Hc * H; i += threads) {
+        const int hl = i / H, g = i - hl * H;
+        const int h = h_first + hl;
+        sT[i] = h < H ? (talk ? talk[(size_t)h * H + g] : (h == g ? 1.0f : 0.0f)) : 0.0f;
+    }
+
+    const int r_lo = lane >> 2, r_hi = r_lo + 8;
+    const int pos_lo = pos0 + r_lo, pos_hi = pos0 + r_hi;
+    const int wlo_lo = (window > 0 && pos_lo + 1 > window) ? pos_lo + 1 - window : 0;
+    const int wlo_hi = (window > 0 && pos_hi + 1 > window) ? pos_hi + 1 - window : 0;
+    const bool valid_lo = r_lo < nq, valid_hi = r_hi < nq;
+
+    float o[HPW][NT_O][4], m_lo[HPW], m_hi[HPW], l_lo[HPW], l_hi[HPW];
+#pragma unroll
+    for (int x = 0; x < HPW; ++x) {
+        const int h = h_first + warp * HPW + x;
+        // without key splits the sink starts the running softmax: its logit as the maximum, a mass of 1
+        const bool start = sink != nullptr && splits == 1 && h < H;
+        m_lo[x] = m_hi[x] = start ? sink[h] * TALK_LOG2E : -INFINITY;
+        l_lo[x] = l_hi[x] = (start && (lane & 3) == 0) ? 1.0f : 0.0f;       // a row's mass is summed over its quad at the end
+#pragma unroll
+        for (int j = 0; j < NT_O; ++j) o[x][j][0] = o[x][j][1] = o[x][j][2] = o[x][j][3] = 0.0f;
+    }
+    const int ksteps = dk / 16;
+    const int id = lane >> 3, rr = lane & 7;
+
+    for (int kt = kt0; kt < kt1; ++kt) {
+        const int key0 = kt * TK;
+        __syncthreads();                        // the tile before is used up (and, the first time, Q and T are written)
+        const int kparts = dk / 8, vparts = DV / 8;
+        for (int i = tid; i < G * TK * kparts; i += threads) {
+            const int part = i % kparts, key = (i / kparts) % TK, g = i / (kparts * TK);
+            const int j = key0 + key;
+            __nv_bfloat16* dst = sK + ((size_t)g * TK + key) * KS + part * 8;
+            if (j >= lo_all && j < hi_all) {
+                const size_t page = (size_t)table[j / page_size];
+                cp_async16(dst, k_pages + ((page * G + g) * page_size + (size_t)(j % page_size)) * dk + part * 8);
+            } else {
+                *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+            }
+        }
+        for (int i = tid; i < G * TK * vparts; i += threads) {
+            const int part = i % vparts, key = (i / vparts) % TK, g = i / (vparts * TK);
+            const int j = key0 + key;
+            __nv_bfloat16* dst = sV + ((size_t)g * TK + key) * VS + part * 8;
+            if (j >= lo_all && j < hi_all) {
+                const size_t page = (size_t)table[j / page_size];
+                cp_async16(dst, v_pages + ((page * G + g) * page_size + (size_t)(j % page_size)) * DV + part * 8);
+            } else {
+                *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+            }
+        }
+        cp_async_commit();
+        cp_async_wait<0>();
+        __syncthreads();
+
+        // raw scores of the heads this warp takes in this phase
+        float s[2][NT_S][4];
+#pragma unroll
+        for (int x = 0; x < 2; ++x) {
+            const int g = warp + NW * x;
+#pragma unroll
+            for (int j = 0; j < NT_S; ++j) s[x][j][0] = s[x][j][1] = s[x][j][2] = s[x][j][3] = 0.0f;
+            if (g < H) {
+                const __nv_bfloat16* tQ = sQ + (size_t)g * 16 * KS;
+                const __nv_bfloat16* tK = sK + (size_t)(g / rep) * TK * KS;
+                for (int ks = 0; ks < ksteps; ++ks) {
+                    uint32_t qf[4];
+                    ldmatrix_x4(qf[0], qf[1], qf[2], qf[3], tQ + ((id & 1) * 8 + rr) * KS + ks * 16 + (id >> 1) * 8);
+#pragma unroll
+                    for (int jp = 0; jp < NT_S / 2; ++jp) {
+                        uint32_t b0, b1, b2, b3;
+                        ldmatrix_x4(b0, b1, b2, b3, tK + (jp * 16 + (id >> 1) * 8 + rr) * KS + ks * 16 + (id & 1) * 8);
+                        mma_bf16(s[x][jp * 2], qf, b0, b1);
+                        mma_bf16(s[x][jp * 2 + 1], qf, b2, b3);
+                    }
+                }
+            }
+        }
+        __syncthreads();                        // every warp is done with the keys: the raw scores take their place
+#pragma unroll
+        for (int x = 0; x < 2; ++x) {
+            const int g = warp + NW * x;
+            if (g < H) {
+                float* rg = sRaw + (size_t)g * 16 * RS;
+#pragma unroll
+                for (int j = 0; j < NT_S; ++j) {
+                    const int c = j * 8 + (lane & 3) * 2;
+                    *reinterpret_cast<float2*>(rg + r_lo * RS + c) = make_float2(s[x][j][0] * scale, s[x][j][1] * scale);
+                    *reinterpret_cast<float2*>(rg + r_hi * RS + c) = make_float2(s[x][j][2] * scale, s[x][j][3] * scale);
+                }
+            }
+        }
+        __syncthreads();
+
+#pragma unroll
+        for (int x = 0; x < HPW; ++x) {
+            const int hl = warp * HPW + x, h = h_first + hl;
+            if (hl >= Hc || h >= H) continue;
+            float mx[NT_S][4];
+#pragma unroll
+            for (int j = 0; j < NT_S; ++j) mx[j][0] = mx[j][1] = mx[j][2] = mx[j][3] = 0.0f;
+            const float* th = sT + (size_t)hl * H;
+            for (int g = 0; g < H; ++g) {
+                const float t = th[g];
+                const float* rg = sRaw + (size_t)g * 16 * RS + (lane & 3) * 2;
+#pragma unroll
+                for (int j = 0; j < NT_S; ++j) {
+                    const float2 a = *reinterpret_cast<const float2*>(rg + r_lo * RS + j * 8);
+                    const float2 b = *reinterpret_cast<const float2*>(rg + r_hi * RS + j * 8);
+                    mx[j][0] = fmaf(t, a.x, mx[j][0]); mx[j][1] = fmaf(t, a.y, mx[j][1]);
+                    mx[j][2] = fmaf(t, b.x, mx[j][2]); mx[j][3] = fmaf(t, b.y, mx[j][3]);
+                }
+            }
+            float new_lo = m_lo[x], new_hi = m_hi[x];
+#pragma unroll
+            for (int j = 0; j < NT_S; ++j)
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
+                    const int key = key0 + j * 8 + (lane & 3) * 2 + c;
+                    const bool ok_lo = valid_lo && key <= pos_lo && key >= wlo_lo;
+                    const bool ok_hi = valid_hi && key <= pos_hi && key >= wlo_hi;
+                    mx[j][c] = ok_lo ? mx[j][c] * TALK_LOG2E : -INFINITY;
+                    mx[j][2 + c] = ok_hi ? mx[j][2 + c] * TALK_LOG2E : -INFINITY;
+                    new_lo = fmaxf(new_lo, mx[j][c]);
+                    new_hi = fmaxf(new_hi, mx[j][2 + c]);
+                }
+            new_lo = fmaxf(new_lo, __shfl_xor_sync(0xffffffffu, new_lo, 1));
+            new_lo = fmaxf(new_lo, __shfl_xor_sync(0xffffffffu, new_lo, 2));
+            new_hi = fmaxf(new_hi, __shfl_xor_sync(0xffffffffu, new_hi, 1));
+            new_hi = fmaxf(new_hi, __shfl_xor_sync(0xffffffffu, new_hi, 2));
+            const float ref_lo = new_lo == -INFINITY ? 0.0f : new_lo, ref_hi = new_hi == -INFINITY ? 0.0f : new_hi;
+            const float a_lo = exp2f(m_lo[x] - ref_lo), a_hi = exp2f(m_hi[x] - ref_hi);       // a maximum of -inf gives 0
+            m_lo[x] = new_lo;
+            m_hi[x] = new_hi;
+            uint32_t pf[TK / 16][4];
+            float sum_lo = 0.0f, sum_hi = 0.0f;
+#pragma unroll
+            for (int j = 0; j < NT_S; ++j) {
+                const float p0 = exp2f(mx[j][0] - ref_lo), p1 = exp2f(mx[j][1] - ref_lo);
+                const float p2 = exp2f(mx[j][2] - ref_hi), p3 = exp2f(mx[j][3] - ref_hi);
+                sum_lo += p0 + p1;
+                sum_hi += p2 + p3;
+                pf[j >> 1][(j & 1) * 2] = pack_bf16(p0, p1);
+                pf[j >> 1][(j & 1) * 2 + 1] = pack_bf16(p2, p3);
+            }
+            l_lo[x] = l_lo[x] * a_lo + sum_lo;
+            l_hi[x] = l_hi[x] * a_hi + sum_hi;
+#pragma unroll
+            for (int j = 0; j < NT_O; ++j) {
+                o[x][j][0] *= a_lo; o[x][j][1] *= a_lo; o[x][j][2] *= a_hi; o[x][j][3] *= a_hi;
+            }
+            const __nv_bfloat16* tV = sV + (size_t)(h / rep) * TK * VS;
+#pragma unroll
+            for (int ks = 0; ks < TK / 16; ++ks)
+#pragma unroll
+                for (int jp = 0; jp < NT_O / 2; ++jp) {
+                    uint32_t b0, b1, b2, b3;
+                    ldmatrix_x4_trans(b0, b1, b2, b3, tV + (ks * 16 + (id & 1) * 8 + rr) * VS + (jp * 2 + (id >> 1)) * 8);
+                    mma_bf16(o[x][jp * 2], pf[ks], b0, b1);
+                    mma_bf16(o[x][jp * 2 + 1], pf[ks], b2, b3);
+                }
+        }
+    }
+#pragma unroll
+    for (int x = 0; x < HPW; ++x) {
+        const int hl = warp * HPW + x, h = h_first + hl;
+        if (hl >= Hc || h >= H) continue;
+        float ll = l_lo[x], lh = l_hi[x];
+        ll += __shfl_xor_sync(0xffffffffu, ll, 1);
+        ll += __shfl_xor_sync(0xffffffffu, ll, 2);
+        lh += __shfl_xor_sync(0xffffffffu, lh, 1);
+        lh += __shfl_xor_sync(0xffffffffu, lh, 2);
+        if (splits == 1) {
+            const float i_lo = ll > 0.0f ? 1.0f / ll : 0.0f, i_hi = lh > 0.0f ? 1.0f / lh : 0.0f;
+#pragma unroll
+            for (int j = 0; j < NT_O; ++j) {
+                const int c = j * 8 + (lane & 3) * 2;
+                if (valid_lo) *reinterpret_cast<uint32_t*>(out + ((size_t)(t0 + r_lo) * H + h) * DV + c) = pack_bf16(o[x][j][0] * i_lo, o[x][j][1] * i_lo);
+                if (valid_hi) *reinterpret_cast<uint32_t*>(out + ((size_t)(t0 + r_hi) * H + h) * DV + c) = pack_bf16(o[x][j][2] * i_hi, o[x][j][3] * i_hi);
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < NT_O; ++j) {
+                const int c = j * 8 + (lane & 3) * 2;
+                if (valid_lo) *reinterpret_cast<float2*>(part_o + ((((size_t)(t0 + r_lo) * H + h) * splits + split) * DV + c)) = make_float2(o[x][j][0], o[x][j][1]);
+                if (valid_hi) *reinterpret_cast<float2*>(part_o + ((((size_t)(t0 + r_hi) * H + h) * splits + split) * DV + c)) = make_float2(o[x][j][2], o[x][j][3]);
+            }
+            if ((lane & 3) == 0) {
+                // the merge works with natural exponents
+                if (valid_lo) {
+                    float* ml = part_ml + (((size_t)(t0 + r_lo) * H + h) * splits + split) * 2;
+                    ml[0] = m_lo[x] / TALK_LOG2E;
+                    ml[1] = ll;
+                }
+                if (valid_hi) {
+                    float* ml = part_ml + (((size_t)(t0 + r_hi) * H + h) * splits + split) * 2;
+                    ml[0] = m_hi[x] / TALK_LOG2E;
+                    ml[1] = lh;
+                }
+            }
+        }
+    }
+}
+
+// How the tensor-core kernel would run these sizes: heads per warp, head groups (grid.y), warps, keys per tile and shared
+// memory; false when it does not take them.
+struct TalkPlan {
+    int hpw, groups, hc, warps, tk;
+    size_t smem;
+};
+static bool talk_plan(int H, int G, int dk, int dv, TalkPlan& p) {
+    if (H < 1 || G < 1 || H % G || dk % 16 || dk < 16 || dk > 256 || !(dv == 32 || dv == 64 || dv == 96 || dv == 128) || H > 32) return false;
+    p.hpw = dv <= 64 ? 2 : 1;
+    p.groups = (p.hpw == 1 && H > 16) ? 2 : 1;
+    p.hc = (H + p.groups - 1) / p.groups;
+    p.warps = (p.hc + p.hpw - 1) / p.hpw;
+    if (p.warps > 16 || (H + p.warps - 1) / p.warps > 2) return false;
+    for (int tk = 32; tk >= 16; tk /= 2) {
+        const size_t q = (size_t)H * 16 * (dk + 8) * 2, k = (size_t)G * tk * (dk + 8) * 2, raw = (size_t)H * 16 * (tk + 8) * 4;
+        const size_t kr = ((k > raw ? k : raw) + 15) & ~(size_t)15;
+        const size_t smem = q + kr + (size_t)G * tk * (dv + 8) * 2 + (size_t)p.hc * H * 4;
+        if (smem <= 227 * 1024) {
+            p.tk = tk;
+            p.smem = smem;
+            return true;
+        }
+    }
+    return false;
+}
+
+MM_EXPORT int mm_attention_talking_mma_supported(int H, int G, int dk, int dv) {
+    TalkPlan p;
+    return talk_plan(H, G, dk, dv, p) ? 1 : 0;
+}
+
+template <int DV, int HPW, int TK>
+static void talk_mma_launch(const TalkPlan& p, dim3 grid, cudaStream_t s, const void* q, const void* k_pages, const void* v_pages, void* out,
+                            void* part_o, void* part_ml, const void* tiles, const void* positions, const void* token_req, const void* block_table,
+                            int table_width, int page_size, int H, int G, int dk, int window, float scale, const void* talk, const void* sink) {
+    auto kernel = attention_talking_mma_kernel<DV, HPW, TK>;
+    if (p.smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)p.smem);
+    mm_launch(kernel, grid, dim3(p.warps * 32), p.smem, s, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages,
+              (__nv_bfloat16*)out, (float*)part_o, (float*)part_ml, (const int32_t*)tiles, (const int32_t*)positions, (const int32_t*)token_req,
+              (const int32_t*)block_table, table_width, page_size, H, G, dk, p.hc, window, scale, (const float*)talk, (const float*)sink);
+}
+
+// tiles [n_tiles, 2] int32 = (first token, tokens <= 16) of one request each; out [n, H * dv] bfloat16.  splits > 1: the
+// key tiles of a tile of tokens are shared out over that many CTAs (part_o fp32 [n, H, splits, dv], part_ml fp32
+// [n, H, splits, 2]) and the merge kernel finishes every row.
+MM_EXPORT int mm_attention_talking_mma(const void* q, const void* k_pages, const void* v_pages, void* out, void* part_o, void* part_ml, int splits,
+                                       const void* tiles, int n_tiles, int n_tokens, const void* positions, const void* token_req,
+                                       const void* block_table, int table_width, int page_size, int H, int G, int dk, int dv, int window,
+                                       float scale, const void* talk, const void* sink, void* stream) {
+    TalkPlan p;
+    MM_REQUIRE(talk_plan(H, G, dk, dv, p), "attention with mixed heads: the tensor-core kernel does not take these sizes");
+    MM_REQUIRE(page_size > 0 && table_width > 0 && window >= 0 && n_tiles >= 0, "attention: bad page geometry or window");
+    MM_REQUIRE(splits >= 1 && splits <= 65535 && (splits == 1 || (part_o != nullptr && part_ml != nullptr)), "attention: key splits need their scratch");
+    if (n_tiles == 0) return MM_OK;
+    cudaStream_t s = (cudaStream_t)stream;
+    const dim3 grid(n_tiles, p.groups, splits);
+#define TALK_MMA(DV, HPW)                                                                                                                          \
+    do {                                                                                                                                           \
+        if (p.tk == 32)                                                                                                                            \
+            talk_mma_launch<DV, HPW, 32>(p, grid, s, q, k_pages, v_pages, out, part_o, part_ml, tiles, positions, token_req, block_table, table_width, \
+                                         page_size, H, G, dk, window, scale, talk, sink);                                                         \
+        else                                                                                                                                       \
+            talk_mma_launch<DV, HPW, 16>(p, grid, s, q, k_pages, v_pages, out, part_o, part_ml, tiles, positions, token_req, block_table, table_width, \
+                                         page_size, H, G, dk, window, scale, talk, sink);                                                         \
+    } while (0)
+    if (dv == 32) TALK_MMA(32, 2);
+    else if (dv == 64) TALK_MMA(64, 2);
+    else if (dv == 96) TALK_MMA(96, 1);
+    else TALK_MMA(128, 1);
+#undef TALK_MMA
+    MM_CHECK_LAUNCH();
+    if (splits > 1) {
+        mm_launch(attention_talking_merge_kernel<__nv_bfloat16>, dim3(n_tokens * H), dim3(128), 0, s, (const float*)part_o, (const float*)part_ml,
+                  (__nv_bfloat16*)out, splits, H, dv, (const float*)sink);
+        MM_CHECK_LAUNCH();
+    }
     return MM_OK;
 }

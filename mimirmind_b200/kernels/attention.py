@@ -265,11 +265,75 @@ def talking_splits(n_tokens: int, window: int, max_kv_len: int, dtype) -> int:
     return max(1, min(-(-TALKING_TARGET_CTAS // n_tokens), -(-keys // 128), TALKING_MAX_SPLITS))
 
 
+USE_TALKING_MMA = True       # False: the attention with mixed heads always runs the fp32-arithmetic kernel (tests compare the two)
+TALKING_TILE_ROWS = 16
+_talking_declared = False
+
+
+def _talking_lib():
+    global _talking_declared
+    from ctypes import c_float, c_int, c_void_p
+    from . import lib as _lib
+    if not _talking_declared:
+        P, I, F = c_void_p, c_int, c_float
+        _lib.declare("mm_attention_talking_mma_supported", [I, I, I, I])
+        _lib.declare("mm_attention_talking_mma", [P, P, P, P, P, P, I, P, I, I, P, P, P, I, I, I, I, I, I, I, F, P, P, P])
+        _talking_declared = True
+    return _lib.load()
+
+
+def talking_plan(ctx):
+    """The step's tokens cut once, on the host, into tiles of at most 16 consecutive tokens of one request; a tile names
+    tokens, not positions (the kernel reads those from the device), so a captured step replays the same plan.  Returns
+    (tiles [n, 2] on the device, n)."""
+    key = ("talking_attention_plan",)
+    plan = ctx.plans.get(key)
+    if plan is None:
+        tiles = []
+        for r in range(ctx.n_requests):
+            s, n, kv = ctx.q_start[r], ctx.q_len[r], ctx.kv_len[r]
+            for off in range(0, n, TALKING_TILE_ROWS):
+                rows = min(TALKING_TILE_ROWS, n - off)
+                tiles.append((kv - n + off + rows, s + off, rows))
+        tiles.sort(key=lambda t: -t[0])           # the tiles with the most keys start first
+        host = torch.tensor([t[1:] for t in tiles], dtype=torch.int32).reshape(-1, 2).pin_memory()
+        plan = ctx.plans[key] = (host.to(ctx.positions.device, non_blocking=True), len(tiles))
+        ctx.plans[key + ("staged",)] = host
+    return plan
+
+
 def paged_talking_attention(q, cache, out, ctx, num_heads: int, num_kv_heads: int, key_dim: int, value_dim: int, window: int,
                             scale: float, talk, sink) -> torch.Tensor:
     """Attention whose scaled scores are mixed between the heads before the softmax (``talk`` [H, H] or None), with a
-    learned sink per head (or None), over pools of keys ``[pages, G, page, key_dim]`` and values ``[pages, G, page, value_dim]``."""
+    learned sink per head (or None), over pools of keys ``[pages, G, page, key_dim]`` and values ``[pages, G, page, value_dim]``.
+    bfloat16 with sizes the tensor-core kernel takes: that kernel, for portions and single tokens alike, its key tiles shared
+    out over several CTAs while the step has few tiles of tokens; anything else, and the 32-bit mode: the fp32-arithmetic kernel."""
     n = q.shape[0]
+    k_pages, v_pages = cache.arrays["k"], cache.arrays["v"]
+    if USE_TALKING_MMA and q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and \
+            _talking_lib().mm_attention_talking_mma_supported(num_heads, num_kv_heads, key_dim, value_dim):
+        from .lib import check
+        lib = _talking_lib()
+        tiles, n_tiles = talking_plan(ctx)
+        keys = min(window, ctx.max_kv_len) if window > 0 else ctx.max_kv_len
+        splits = 1
+        if n_tiles < TALKING_TARGET_CTAS // 2:
+            splits = max(1, min(-(-TALKING_TARGET_CTAS // n_tiles), -(-keys // 128), TALKING_MAX_SPLITS))
+        part_o = part_ml = None
+        if splits > 1:
+            skey = ("talking_attention_scratch", n, num_heads, splits, value_dim)
+            if skey not in ctx.plans:
+                ctx.plans[skey] = (torch.empty((n, num_heads, splits, value_dim), dtype=torch.float32, device=q.device),
+                                   torch.empty((n, num_heads, splits, 2), dtype=torch.float32, device=q.device))
+            part_o, part_ml = ctx.plans[skey]
+        check(lib.mm_attention_talking_mma(q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), out.data_ptr(),
+                                           part_o.data_ptr() if part_o is not None else None,
+                                           part_ml.data_ptr() if part_ml is not None else None, splits, tiles.data_ptr(), n_tiles, n,
+                                           ctx.positions.data_ptr(), ctx.token_req.data_ptr(), cache.block_table.data_ptr(),
+                                           cache.block_table.shape[1], cache.page_size, num_heads, num_kv_heads, key_dim, value_dim, int(window),
+                                           float(scale), talk.data_ptr() if talk is not None else None,
+                                           sink.data_ptr() if sink is not None else None, ops._stream()), "attention_talking_mma")
+        return out
     splits = talking_splits(n, window, ctx.max_kv_len, q.dtype)
     scratch = None
     if splits > 1:
@@ -278,5 +342,5 @@ def paged_talking_attention(q, cache, out, ctx, num_heads: int, num_kv_heads: in
             ctx.plans[skey] = (torch.empty((n, num_heads, splits, value_dim), dtype=torch.float32, device=q.device),
                                torch.empty((n, num_heads, splits, 2), dtype=torch.float32, device=q.device))
         scratch = ctx.plans[skey]
-    return ops.attention_talking(q, cache.arrays["k"], cache.arrays["v"], out, ctx.positions, ctx.token_req, cache.block_table, cache.page_size,
+    return ops.attention_talking(q, k_pages, v_pages, out, ctx.positions, ctx.token_req, cache.block_table, cache.page_size,
                                  num_heads, num_kv_heads, key_dim, value_dim, window, scale, talk, sink, splits=splits, scratch=scratch)

@@ -74,9 +74,20 @@ def _attend(q, kp, vp, table, page, lo, hi, H, G, dk, dv, scale, dtype, talk, si
     return np.concatenate(outs, 0)
 
 
+@pytest.fixture(params=[True, False], ids=["tensor-cores", "fp32-arithmetic"])
+def route(request, monkeypatch):
+    """Both kernels of the attention with mixed heads: sizes the tensor-core kernel takes run it, or never."""
+    from mimirmind_b200.kernels import attention
+    monkeypatch.setattr(attention, "USE_TALKING_MMA", request.param)
+    return request.param
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("H,G,dk,dv,page", [(4, 2, 24, 16, 16), (3, 3, 9, 7, 8), (8, 2, 64, 64, 16), (5, 1, 96, 32, 32), (1, 1, 10, 12, 16), (16, 4, 128, 64, 16)])
-def test_mixed_heads_attention_against_the_plain_one(H, G, dk, dv, page, dtype):
+@pytest.mark.parametrize("H,G,dk,dv,page", [(4, 2, 24, 16, 16), (3, 3, 9, 7, 8), (8, 2, 64, 64, 16), (5, 1, 96, 32, 32), (1, 1, 10, 12, 16), (16, 4, 128, 64, 16),
+                                            (6, 6, 96, 96, 16), (32, 8, 128, 128, 16), (20, 4, 64, 128, 8), (3, 1, 32, 64, 64)])
+def test_mixed_heads_attention_against_the_plain_one(H, G, dk, dv, page, dtype, route):
+    if dtype == "float32" and not route:
+        pytest.skip("the 32-bit mode has one route")
     rng = np.random.RandomState(H * 100 + dk)
     T = 300
     q, k, v = rng.randn(T, H, dk), rng.randn(T, G, dk), rng.randn(T, G, dv)
@@ -98,7 +109,7 @@ def test_mixed_heads_attention_against_the_plain_one(H, G, dk, dv, page, dtype):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("dk,dv", [(16, 8), (64, 64), (96, 32)])
-def test_one_key_that_stands_out(dk, dv, dtype):
+def test_one_key_that_stands_out(dk, dv, dtype, route):
     """One key answers one query direction with a score far above the rest: the query's result is that key's value, at the
     sequence's start, on both sides of page borders, hundreds of tokens back, in a portion, in a portion of two tokens and
     for a single token; through another head when the mixing matrix swaps heads; and not at all one token outside a window."""
@@ -131,8 +142,8 @@ def test_one_key_that_stands_out(dk, dv, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_the_learned_sink_takes_its_share(dtype):
-    H, G, dk, dv, page, T = 3, 3, 32, 16, 16, 90
+def test_the_learned_sink_takes_its_share(dtype, route):
+    H, G, dk, dv, page, T = 3, 3, 32, 32, 16, 90
     rng = np.random.RandomState(3)
     q, k, v = rng.randn(T, H, dk), rng.randn(T, G, dk), rng.randn(T, G, dv)
     if dtype == "bfloat16":
