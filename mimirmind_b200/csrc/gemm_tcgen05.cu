@@ -137,12 +137,23 @@ __device__ __forceinline__ void epilogue_rows(uint32_t taddr, int m0, int n0, in
                         *reinterpret_cast<uint4*>(srow + (((cc * 4 + i) ^ (lane & 15)) << 4)) =
                             make_uint4(pack2(v[i * 8], v[i * 8 + 1]), pack2(v[i * 8 + 2], v[i * 8 + 3]), pack2(v[i * 8 + 4], v[i * 8 + 5]), pack2(v[i * 8 + 6], v[i * 8 + 7]));
                 } else {
-                    // columns: 8 gate, 8 up, 8 gate, 8 up  ->  16 outputs
+                    // columns: 8 gate, 8 up, 8 gate, 8 up  ->  16 outputs.  Another gated activation than silu(g) u is named in
+                    // bias_dtype's bits from 8 on (glu_act's kinds), its limit travels as the bits of the unused bias pointer.
                     float a[16];
+                    const int glu = bias_dtype >> 8;
+                    if (glu != 0) {
+                        const float limit = __uint_as_float((uint32_t)(uintptr_t)bias);
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        a[i] = silu_mul(v[i], v[8 + i]);
-                        a[8 + i] = silu_mul(v[16 + i], v[24 + i]);
+                        for (int i = 0; i < 8; ++i) {
+                            a[i] = glu_act<false>(v[i], v[8 + i], glu, limit, 1.0f);
+                            a[8 + i] = glu_act<false>(v[16 + i], v[24 + i], glu, limit, 1.0f);
+                        }
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            a[i] = silu_mul(v[i], v[8 + i]);
+                            a[8 + i] = silu_mul(v[16 + i], v[24 + i]);
+                        }
                     }
 #pragma unroll
                     for (int i = 0; i < 2; ++i)
@@ -478,7 +489,8 @@ int launch(const CUtensorMap& a, const CUtensorMap& b, void* out, const void* bi
 
 template <int EPI>
 int launch_grouped(const CUtensorMap& a, const CUtensorMap& b, void* out, int M, int N, int K, int ldo, int* err, int max_ctas,
-                   const int32_t* group_tiles, const int32_t* n_group_tiles, int max_group_tiles, int group_w_rows, cudaStream_t s) {
+                   const int32_t* group_tiles, const int32_t* n_group_tiles, int max_group_tiles, int group_w_rows, cudaStream_t s, int glu = 0,
+                   float limit = 0.0f) {
     const size_t smem = (size_t)STAGES * STAGE_BYTES + 4 * EPI_STAGE_BYTES + 1024 + sizeof(SharedCtl);
     static bool configured = false;
     if (!configured) {
@@ -490,7 +502,10 @@ int launch_grouped(const CUtensorMap& a, const CUtensorMap& b, void* out, int M,
     }
     const long long total = (long long)max_group_tiles * ((N + BN - 1) / BN);
     const int grid = total < max_ctas ? (int)total : max_ctas;
-    gemm_tcgen05_kernel<EPI><<<grid, GEMM_THREADS, smem, s>>>(a, b, out, nullptr, MM_F32, M, N, K, ldo, err, group_tiles, n_group_tiles, group_w_rows);
+    uint32_t limit_bits;
+    memcpy(&limit_bits, &limit, sizeof(limit_bits));
+    gemm_tcgen05_kernel<EPI><<<grid, GEMM_THREADS, smem, s>>>(a, b, out, glu ? (const void*)(uintptr_t)limit_bits : nullptr, MM_F32 | (glu << 8), M, N, K, ldo,
+                                                              err, group_tiles, n_group_tiles, group_w_rows);
     MM_CHECK_LAUNCH();
     return MM_OK;
 }
@@ -501,8 +516,11 @@ int launch_grouped(const CUtensorMap& a, const CUtensorMap& b, void* out, int M,
 // matrices one after the other; tile i of the device-made list `group_tiles` (3 ints each: first row, end row, group; at
 // most 128 rows, never across a group's border; `n_group_tiles` of them, at most `max_group_tiles`) is multiplied with
 // its group's matrix.  out [M, ldo]: bf16 [M, N], or with the SwiGLU epilogue bf16 [M, N/2].
-MM_EXPORT int mm_gemm_tcgen05_grouped(const void* A, const void* W, void* out, int epilogue, int M, int groups, int N, int K, int lda, int ldo,
-                                      const void* group_tiles, const void* n_group_tiles, int max_group_tiles, void* err, void* stream) {
+// glu, limit: another gated activation than silu(g) u in the SwiGLU epilogue (glu_act's kinds in common.cuh).
+MM_EXPORT int mm_gemm_tcgen05_grouped_act(const void* A, const void* W, void* out, int epilogue, int M, int groups, int N, int K, int lda, int ldo,
+                                          const void* group_tiles, const void* n_group_tiles, int max_group_tiles, int glu, float limit, void* err,
+                                          void* stream) {
+    MM_REQUIRE(glu == 0 || (epilogue == EPI_SWIGLU && glu == MM_GLU_CLAMPED), "gemm_tcgen05 grouped: the gated activations are silu and the clamped form, in the SwiGLU epilogue");
     MM_REQUIRE(M > 0 && N > 0 && K > 0 && groups > 0 && max_group_tiles > 0 && group_tiles && n_group_tiles, "gemm_tcgen05 grouped: bad sizes");
     MM_REQUIRE(K % 8 == 0 && lda % 8 == 0 && lda >= K, "gemm_tcgen05: K and the row stride of A must be multiples of 8 (16-byte TMA rows)");
     MM_REQUIRE(((uintptr_t)A & 15) == 0 && ((uintptr_t)W & 15) == 0 && ((uintptr_t)out & 15) == 0, "gemm_tcgen05: pointers must be 16-byte aligned");
@@ -520,9 +538,14 @@ MM_EXPORT int mm_gemm_tcgen05_grouped(const void* A, const void* W, void* out, i
     cudaStream_t s = (cudaStream_t)stream;
     if (epilogue == EPI_SWIGLU)
         return launch_grouped<EPI_SWIGLU>(ta, tb, out, M, N, K, ldo, (int*)err, sms, (const int32_t*)group_tiles, (const int32_t*)n_group_tiles,
-                                          max_group_tiles, N, s);
+                                          max_group_tiles, N, s, glu, limit);
     return launch_grouped<EPI_BF16>(ta, tb, out, M, N, K, ldo, (int*)err, sms, (const int32_t*)group_tiles, (const int32_t*)n_group_tiles,
                                     max_group_tiles, N, s);
+}
+
+MM_EXPORT int mm_gemm_tcgen05_grouped(const void* A, const void* W, void* out, int epilogue, int M, int groups, int N, int K, int lda, int ldo,
+                                      const void* group_tiles, const void* n_group_tiles, int max_group_tiles, void* err, void* stream) {
+    return mm_gemm_tcgen05_grouped_act(A, W, out, epilogue, M, groups, N, K, lda, ldo, group_tiles, n_group_tiles, max_group_tiles, 0, 0.0f, err, stream);
 }
 
 // A [M, lda] bf16 (K leading columns used), W [N, K] bf16, out [M, ldo] (bf16, fp32, or with the SwiGLU epilogue bf16

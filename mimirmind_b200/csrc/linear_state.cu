@@ -647,12 +647,14 @@ MM_EXPORT int mm_forget_gate_prep(void* x, int ld, int n_tokens, int q_off, int 
     return MM_OK;
 }
 
-// The walk: q, f fp32 rows with H heads of dk (row strides ldq, ldf), v with H heads of dv.  A block of 8 warps owns 32
-// columns of one head's S for one request, a warp four of them, a lane the entries lane, lane + 32, ... of each; q, f and
-// v of FG_AHEAD tokens at a time are staged in shared memory.  The state's layout in a slot is [H, dv, dk], as in the walk
+// The walk: q, f fp32 rows with H heads of dk (row strides ldq, ldf), v with H heads of dv.  A block of 8 warps owns 8
+// columns of one head's S for one request, a warp one of them (the walk is a chain from token to token: what shortens it is
+// less work per warp and token, and the narrow blocks are many), a lane the entries lane, lane + 32, ... of its column;
+// q, f and v of FG_AHEAD tokens at a time are staged in shared memory.  The state's layout in a slot is [H, dv, dk], as in the walk
 // above; a request at position 0 starts from zero whatever its slot holds.
 #define FG_AHEAD 16
-#define FG_COLS 32
+#define FG_CW 1          // columns per warp
+#define FG_COLS (8 * FG_CW)
 template <int PER>
 __global__ void __launch_bounds__(256) forget_gate_walk_kernel(const float* __restrict__ q, const float* __restrict__ f, const float* __restrict__ v,
                                                                int ldq, int ldf, int ldv, float* __restrict__ out, float* __restrict__ state,
@@ -670,10 +672,10 @@ __global__ void __launch_bounds__(256) forget_gate_walk_kernel(const float* __re
     const int n = req_meta ? req_meta[4 * r + 1] : 1;
     const bool fresh = positions[t0] == 0;
     float* st = state + (size_t)slots[r] * state_stride + (size_t)h * dv * dk;
-    float S[4][PER];
+    float S[FG_CW][PER];
 #pragma unroll
-    for (int c = 0; c < 4; ++c) {
-        const int col = col0 + warp * 4 + c;
+    for (int c = 0; c < FG_CW; ++c) {
+        const int col = col0 + warp * FG_CW + c;
 #pragma unroll
         for (int e = 0; e < PER; ++e) {
             const int i = lane + 32 * e;
@@ -703,8 +705,8 @@ __global__ void __launch_bounds__(256) forget_gate_walk_kernel(const float* __re
                 ff[e] = i < dk ? sf[tt * dk + i] : 1.0f;
             }
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                const float vv = sv[tt * FG_COLS + warp * 4 + c];
+            for (int c = 0; c < FG_CW; ++c) {
+                const float vv = sv[tt * FG_COLS + warp * FG_CW + c];
                 float dot = 0.0f;
 #pragma unroll
                 for (int e = 0; e < PER; ++e) {
@@ -712,7 +714,7 @@ __global__ void __launch_bounds__(256) forget_gate_walk_kernel(const float* __re
                     dot = fmaf(S[c][e], qq[e], dot);
                 }
                 dot = warp_sum(dot);
-                if (lane == 0) so[tt * FG_COLS + warp * 4 + c] = dot;
+                if (lane == 0) so[tt * FG_COLS + warp * FG_CW + c] = dot;
             }
         }
         __syncthreads();
@@ -722,8 +724,8 @@ __global__ void __launch_bounds__(256) forget_gate_walk_kernel(const float* __re
         }
     }
 #pragma unroll
-    for (int c = 0; c < 4; ++c) {
-        const int col = col0 + warp * 4 + c;
+    for (int c = 0; c < FG_CW; ++c) {
+        const int col = col0 + warp * FG_CW + c;
         if (col >= dv) continue;
 #pragma unroll
         for (int e = 0; e < PER; ++e) {

@@ -636,6 +636,34 @@ MM_EXPORT int mm_moe_gemm(const void* A, int a_dtype, int lda, const void* W, in
                            0, 0.0f, nullptr, stream);
 }
 
+// The step's rows copied into sorted order, each multiplied by its (token, choice)'s weight and rounded to the rows'
+// dtype: out[i] = x[row_token[i]] * wts[order[i]] (wts null: a plain copy).
+template <typename T>
+__global__ void moe_gather_scaled_kernel(const T* __restrict__ x, const int32_t* __restrict__ row_token, const int32_t* __restrict__ order,
+                                         const float* __restrict__ wts, T* __restrict__ out, int d) {
+    const size_t i = blockIdx.x;
+    const T* src = x + (size_t)row_token[i] * d;
+    const float s = wts ? wts[order[i]] : 1.0f;
+    for (int c = threadIdx.x; c < d; c += blockDim.x) out[i * d + c] = from_f32<T>(to_f32<T>(src[c]) * s);
+}
+
+MM_EXPORT int mm_moe_gather_scaled(const void* x, int dtype, const void* row_token, const void* order, const void* wts, void* out, int n_rows, int d,
+                                   void* stream) {
+    MM_REQUIRE(n_rows >= 0 && d > 0 && row_token != nullptr && order != nullptr, "moe gather: bad sizes");
+    if (n_rows == 0) return MM_OK;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == MM_BF16)
+        mm_launch(moe_gather_scaled_kernel<__nv_bfloat16>, dim3(n_rows), dim3(256), 0, s, (const __nv_bfloat16*)x, (const int32_t*)row_token,
+                  (const int32_t*)order, (const float*)wts, (__nv_bfloat16*)out, d);
+    else if (dtype == MM_F32)
+        mm_launch(moe_gather_scaled_kernel<float>, dim3(n_rows), dim3(256), 0, s, (const float*)x, (const int32_t*)row_token, (const int32_t*)order,
+                  (const float*)wts, (float*)out, d);
+    else
+        MM_REQUIRE(false, "moe gather: dtype must be float32 or bfloat16");
+    MM_CHECK_LAUNCH();
+    return MM_OK;
+}
+
 // out[t, :] = sum over the token's choices c, in order, of wts[t, c] * y[row(t, c), :], row(t, c) = t * top + c or, when
 // y stands in sorted order, place[t * top + c]
 template <typename TY, typename TO>

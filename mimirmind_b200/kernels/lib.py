@@ -86,6 +86,8 @@ _PROTOTYPES = {
     "mm_head_finish": [P, I, I, F, I, F, F, P, I, P, I, I, I, I, I, P],
     "mm_moe_router_scored": [P, I, I, P, I, I, I, I, I, I, I, P, P, P],
     "mm_moe_gemm_act": [P, I, I, P, I, P, I, I, P, P, I, I, I, I, I, I, I, I, I, F, P, P],
+    "mm_gemm_tcgen05_grouped_act": [P, P, P, I, I, I, I, I, I, I, P, P, I, I, F, P, P],
+    "mm_moe_gather_scaled": [P, I, P, P, P, P, I, I, P],
     "mm_talking_prep": [P, I, I, I, I, P, P, F, P, I, I, P, P, P, I, P, I, I, I, I, I, I, P],
     "mm_attention_talking": [P, P, P, P, I, P, P, I, P, P, P, I, I, I, I, I, I, I, I, F, P, P, P],
     "mm_forget_gate_prep": [P, I, I, I, I, I, I, P, P, P],

@@ -1174,7 +1174,22 @@ def moe_gemm(a: torch.Tensor, w: torch.Tensor, rows: ExpertRows, n_rows: int, to
     return out
 
 
-def moe_gemm_grouped(a: torch.Tensor, w: torch.Tensor, rows: ExpertRows, swiglu: bool) -> torch.Tensor:
+def moe_gather_scaled(x: torch.Tensor, rows: ExpertRows, wts: Optional[torch.Tensor]) -> torch.Tensor:
+    """The step's rows in sorted order, each multiplied by its (token, choice)'s weight (``wts`` fp32 [tokens, top]; None: a
+    plain copy) and rounded to their dtype: what the grouped products of experts that weigh their input read."""
+    _need(x, "moe rows")
+    if rows.row_token is None:
+        raise KernelError("moe gather: the rows were sorted without their tile list")
+    if wts is not None:
+        _need(wts, "moe weights", torch.float32)
+    n_rows = rows.row_token.numel()
+    out = torch.empty((n_rows, x.shape[1]), dtype=x.dtype, device=x.device)
+    check(_lib.load().mm_moe_gather_scaled(x.data_ptr(), dtype_code(x.dtype), rows.row_token.data_ptr(), rows.order.data_ptr(), _ptr(wts),
+                                           out.data_ptr(), n_rows, x.shape[1], _stream()), "moe_gather_scaled")
+    return out
+
+
+def moe_gemm_grouped(a: torch.Tensor, w: torch.Tensor, rows: ExpertRows, swiglu: bool, activation: str = "silu", limit: float = 0.0) -> torch.Tensor:
     """The grouped tensor-memory product: ``a`` [n_rows, K] bf16 in sorted order, ``w`` [E, N, K] bf16; every row tile of
     ``rows.tiles`` times its expert's matrix.  ``swiglu``: the matrix interleaves gate and up rows in blocks of 8 and the
     result is ``silu(gate) * up`` [n_rows, N/2]; else [n_rows, N].  bf16, in sorted order."""
@@ -1185,9 +1200,10 @@ def moe_gemm_grouped(a: torch.Tensor, w: torch.Tensor, rows: ExpertRows, swiglu:
     n_rows, K = a.shape
     E, N, _ = w.shape
     out = torch.empty((n_rows, N // 2 if swiglu else N), dtype=torch.bfloat16, device=a.device)
-    check(_lib.load().mm_gemm_tcgen05_grouped(a.data_ptr(), w.data_ptr(), out.data_ptr(), 1 if swiglu else 0, n_rows, E, N, K, K, out.shape[1],
-                                              rows.tiles.data_ptr(), rows.n_tiles.data_ptr(), rows.max_tiles,
-                                              tcgen05_error_flag(a.device).data_ptr(), _stream()), "gemm_tcgen05_grouped")
+    check(_lib.load().mm_gemm_tcgen05_grouped_act(a.data_ptr(), w.data_ptr(), out.data_ptr(), 1 if swiglu else 0, n_rows, E, N, K, K, out.shape[1],
+                                                  rows.tiles.data_ptr(), rows.n_tiles.data_ptr(), rows.max_tiles,
+                                                  GLU_ACTIVATIONS[activation] if swiglu else 0, float(limit),
+                                                  tcgen05_error_flag(a.device).data_ptr(), _stream()), "gemm_tcgen05_grouped")
     return out
 
 

@@ -101,15 +101,18 @@ class RoutedExperts(FeedForward):
         idx, wts = ops.moe_router(x, self.w_router, self.top, self.groups, self.keep, scoring=self.scoring)
         n_rows = n * self.top
         on_input = self.weight_on == "input"
-        if self.interleaved and n_rows >= GROUPED_MIN_ROWS and not ctx_plain(ctx) and self.activation == "silu" and not on_input:
+        if self.interleaved and n_rows >= GROUPED_MIN_ROWS and not ctx_plain(ctx):
             # prompt-sized: the rows are copied into sorted order once, and both products run on tensor memory over tiles of
             # 128 rows of one expert; the outputs stay in sorted order and the weighted sum fetches them by place
             rows = ops.moe_sort(idx, self.experts, with_tiles=True)
-            sorted_x = torch.empty((n_rows, self.hidden), dtype=x.dtype, device=x.device)
-            ops.gather_rows(x, rows.row_token, sorted_x)
-            hidden = ops.moe_gemm_grouped(sorted_x, self.w_in, rows, swiglu=True)
+            if on_input:        # the weight rides on the copy: expert(w h) with w h rounded to the rows' dtype
+                sorted_x = ops.moe_gather_scaled(x, rows, wts)
+            else:
+                sorted_x = torch.empty((n_rows, self.hidden), dtype=x.dtype, device=x.device)
+                ops.gather_rows(x, rows.row_token, sorted_x)
+            hidden = ops.moe_gemm_grouped(sorted_x, self.w_in, rows, swiglu=True, activation=self.activation, limit=self.limit)
             y = ops.moe_gemm_grouped(hidden, self.w_out, rows, swiglu=False)
-            return ops.moe_combine(y, wts, self.rt.dtype, place=rows.place)
+            return ops.moe_combine(y, None if on_input else wts, self.rt.dtype, place=rows.place, top=self.top)
         rows = ops.moe_sort(idx, self.experts)
         tc = self.rt.matmul != "simt"
         hidden = ops.moe_gemm(x, self.w_in, rows, n_rows, self.top, True, self.rt.dtype, tensor_cores=tc, interleaved=self.interleaved,
