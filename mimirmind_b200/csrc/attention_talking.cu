@@ -440,25 +440,41 @@ __global__ void __launch_bounds__(512) attention_talking_mma_kernel(
         }
         __syncthreads();
 
+        // the mixed scores of the warp's heads: every raw head's tile is read once for all of them
+        float mxs[HPW][NT_S][4];
 #pragma unroll
-        for (int x = 0; x < HPW; ++x) {
-            const int hl = warp * HPW + x, h = h_first + hl;
-            if (hl >= Hc || h >= H) continue;
-            float mx[NT_S][4];
+        for (int x = 0; x < HPW; ++x)
 #pragma unroll
-            for (int j = 0; j < NT_S; ++j) mx[j][0] = mx[j][1] = mx[j][2] = mx[j][3] = 0.0f;
-            const float* th = sT + (size_t)hl * H;
+            for (int j = 0; j < NT_S; ++j) mxs[x][j][0] = mxs[x][j][1] = mxs[x][j][2] = mxs[x][j][3] = 0.0f;
+        if (warp * HPW < Hc) {
+            const float* th = sT + (size_t)warp * HPW * H;
             for (int g = 0; g < H; ++g) {
-                const float t = th[g];
+                float t[HPW];
+#pragma unroll
+                for (int x = 0; x < HPW; ++x) t[x] = (warp * HPW + x < Hc) ? th[x * H + g] : 0.0f;
                 const float* rg = sRaw + (size_t)g * 16 * RS + (lane & 3) * 2;
 #pragma unroll
                 for (int j = 0; j < NT_S; ++j) {
                     const float2 a = *reinterpret_cast<const float2*>(rg + r_lo * RS + j * 8);
-                    const float2 b = *reinterpret_cast<const float2*>(rg + r_hi * RS + j * 8);
-                    mx[j][0] = fmaf(t, a.x, mx[j][0]); mx[j][1] = fmaf(t, a.y, mx[j][1]);
-                    mx[j][2] = fmaf(t, b.x, mx[j][2]); mx[j][3] = fmaf(t, b.y, mx[j][3]);
+#pragma unroll
+                    for (int x = 0; x < HPW; ++x) {
+                        mxs[x][j][0] = fmaf(t[x], a.x, mxs[x][j][0]); mxs[x][j][1] = fmaf(t[x], a.y, mxs[x][j][1]);
+                    }
+                    if (nq > 8) {           // a tile of at most eight tokens (a decode step's) has no second half of rows
+                        const float2 b = *reinterpret_cast<const float2*>(rg + r_hi * RS + j * 8);
+#pragma unroll
+                        for (int x = 0; x < HPW; ++x) {
+                            mxs[x][j][2] = fmaf(t[x], b.x, mxs[x][j][2]); mxs[x][j][3] = fmaf(t[x], b.y, mxs[x][j][3]);
+                        }
+                    }
                 }
             }
+        }
+#pragma unroll
+        for (int x = 0; x < HPW; ++x) {
+            const int hl = warp * HPW + x, h = h_first + hl;
+            if (hl >= Hc || h >= H) continue;
+            float (&mx)[NT_S][4] = mxs[x];
             float new_lo = m_lo[x], new_hi = m_hi[x];
 #pragma unroll
             for (int j = 0; j < NT_S; ++j)
@@ -552,6 +568,9 @@ __global__ void __launch_bounds__(512) attention_talking_mma_kernel(
 
 // How the tensor-core kernel would run these sizes: heads per warp, head groups (grid.y), warps, keys per tile and shared
 // memory; false when it does not take them.
+static int g_talk_prefer16 = 1;
+MM_EXPORT void mm_attention_talking_prefer16(int on) { g_talk_prefer16 = on; }
+
 struct TalkPlan {
     int hpw, groups, hc, warps, tk;
     size_t smem;
@@ -563,17 +582,22 @@ static bool talk_plan(int H, int G, int dk, int dv, TalkPlan& p) {
     p.hc = (H + p.groups - 1) / p.groups;
     p.warps = (p.hc + p.hpw - 1) / p.hpw;
     if (p.warps > 16 || (H + p.warps - 1) / p.warps > 2) return false;
-    for (int tk = 32; tk >= 16; tk /= 2) {
+    // 32 keys per tile where two CTAs of them share an SM or nothing smaller does either; else 16 keys if that gets two CTAs
+    // onto an SM (a CTA of few warps waits on every barrier and copy: a second one fills those gaps) or is all that fits
+    size_t need[2];
+    for (int i = 0; i < 2; ++i) {
+        const int tk = i == 0 ? 32 : 16;
         const size_t q = (size_t)H * 16 * (dk + 8) * 2, k = (size_t)G * tk * (dk + 8) * 2, raw = (size_t)H * 16 * (tk + 8) * 4;
         const size_t kr = ((k > raw ? k : raw) + 15) & ~(size_t)15;
-        const size_t smem = q + kr + (size_t)G * tk * (dv + 8) * 2 + (size_t)p.hc * H * 4;
-        if (smem <= 227 * 1024) {
-            p.tk = tk;
-            p.smem = smem;
-            return true;
-        }
+        need[i] = q + kr + (size_t)G * tk * (dv + 8) * 2 + (size_t)p.hc * H * 4;
     }
-    return false;
+    const size_t whole = 227 * 1024, half = 113 * 1024;
+    if (need[1] > whole) return false;
+    const bool two_of_16 = need[1] <= half && need[0] > half && p.warps <= 16;
+    const bool use16 = need[0] > whole || (two_of_16 && g_talk_prefer16);
+    p.tk = use16 ? 16 : 32;
+    p.smem = use16 ? need[1] : need[0];
+    return true;
 }
 
 MM_EXPORT int mm_attention_talking_mma_supported(int H, int G, int dk, int dv) {

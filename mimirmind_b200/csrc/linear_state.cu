@@ -655,12 +655,18 @@ MM_EXPORT int mm_forget_gate_prep(void* x, int ld, int n_tokens, int q_off, int 
 #define FG_AHEAD 16
 #define FG_CW 1          // columns per warp
 #define FG_COLS (8 * FG_CW)
-template <int PER>
+// MODE 0: a request's tokens from its slot's state, which is left updated.  Long portions are cut into chunks that are walked
+// side by side, because the update is linear in S with a diagonal transition (S_end = diag(product of the f) S_start + what
+// the chunk adds): MODE 1 walks chunk blockIdx.z from zero and leaves what it adds in scratch and the product of its gates per
+// key channel in `gain` [chunks, H * dk]; a carry kernel walks each request's chunks in order, leaves every chunk's starting
+// state in scratch and the last state in the slot; MODE 2 walks every chunk again from its starting state and writes the
+// outputs.
+template <int PER, int MODE>
 __global__ void __launch_bounds__(256) forget_gate_walk_kernel(const float* __restrict__ q, const float* __restrict__ f, const float* __restrict__ v,
                                                                int ldq, int ldf, int ldv, float* __restrict__ out, float* __restrict__ state,
                                                                long long state_stride, const int32_t* __restrict__ req_meta,
                                                                const int32_t* __restrict__ slots, const int32_t* __restrict__ positions, int H,
-                                                               int dk, int dv) {
+                                                               int dk, int dv, float* __restrict__ gain) {
     extern __shared__ float fg_smem[];
     float* sq = fg_smem;                          // [AHEAD][dk]
     float* sf = sq + FG_AHEAD * dk;               // [AHEAD][dk]
@@ -670,8 +676,12 @@ __global__ void __launch_bounds__(256) forget_gate_walk_kernel(const float* __re
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t0 = req_meta ? req_meta[4 * r] : r;
     const int n = req_meta ? req_meta[4 * r + 1] : 1;
-    const bool fresh = positions[t0] == 0;
-    float* st = state + (size_t)slots[r] * state_stride + (size_t)h * dv * dk;
+    const bool fresh = MODE == 1 || (MODE == 0 && positions[t0] == 0);
+    // MODE 1, 2: r is a chunk, req_meta the chunk list, state the scratch with one set of matrices per chunk
+    float* st = state + (size_t)(MODE == 0 ? slots[r] : r) * state_stride + (size_t)h * dv * dk;
+    float prod[PER];
+#pragma unroll
+    for (int e = 0; e < PER; ++e) prod[e] = 1.0f;
     float S[FG_CW][PER];
 #pragma unroll
     for (int c = 0; c < FG_CW; ++c) {
@@ -703,6 +713,7 @@ __global__ void __launch_bounds__(256) forget_gate_walk_kernel(const float* __re
                 const int i = lane + 32 * e;
                 qq[e] = i < dk ? sq[tt * dk + i] : 0.0f;
                 ff[e] = i < dk ? sf[tt * dk + i] : 1.0f;
+                if (MODE == 1) prod[e] *= ff[e];
             }
 #pragma unroll
             for (int c = 0; c < FG_CW; ++c) {
@@ -711,18 +722,29 @@ __global__ void __launch_bounds__(256) forget_gate_walk_kernel(const float* __re
 #pragma unroll
                 for (int e = 0; e < PER; ++e) {
                     S[c][e] = fmaf(ff[e], S[c][e], (1.0f - ff[e]) * vv);
-                    dot = fmaf(S[c][e], qq[e], dot);
+                    if (MODE != 1) dot = fmaf(S[c][e], qq[e], dot);
                 }
-                dot = warp_sum(dot);
-                if (lane == 0) so[tt * FG_COLS + warp * FG_CW + c] = dot;
+                if (MODE != 1) {
+                    dot = warp_sum(dot);
+                    if (lane == 0) so[tt * FG_COLS + warp * FG_CW + c] = dot;
+                }
             }
         }
         __syncthreads();
-        for (int idx = threadIdx.x; idx < cnt * FG_COLS; idx += 256) {
-            const int tt = idx / FG_COLS, c = idx - tt * FG_COLS;
-            if (col0 + c < dv) out[(size_t)(t0 + base + tt) * H * dv + h * dv + col0 + c] = so[idx];
+        if (MODE != 1)
+            for (int idx = threadIdx.x; idx < cnt * FG_COLS; idx += 256) {
+                const int tt = idx / FG_COLS, c = idx - tt * FG_COLS;
+                if (col0 + c < dv) out[(size_t)(t0 + base + tt) * H * dv + h * dv + col0 + c] = so[idx];
+            }
+    }
+    if (MODE == 1 && blockIdx.x == 0 && warp == 0) {
+#pragma unroll
+        for (int e = 0; e < PER; ++e) {
+            const int i = lane + 32 * e;
+            if (i < dk) gain[((size_t)r * H + h) * dk + i] = prod[e];
         }
     }
+    if (MODE == 2) return;
 #pragma unroll
     for (int c = 0; c < FG_CW; ++c) {
         const int col = col0 + warp * FG_CW + c;
@@ -735,6 +757,20 @@ __global__ void __launch_bounds__(256) forget_gate_walk_kernel(const float* __re
     }
 }
 
+template <int MODE>
+static void fg_walk_launch(dim3 grid, cudaStream_t s, const float* q, const float* f, const float* v, int ldq, int ldf, int ldv, float* out, float* state,
+                           long long state_stride, const int32_t* req_meta, const int32_t* slots, const int32_t* positions, int H, int dk, int dv,
+                           float* gain) {
+    const size_t smem = sizeof(float) * FG_AHEAD * (2 * (size_t)dk + 2 * FG_COLS);
+#define FG_LAUNCH(PER) \
+    mm_launch(forget_gate_walk_kernel<PER, MODE>, grid, dim3(256), smem, s, q, f, v, ldq, ldf, ldv, out, state, state_stride, req_meta, slots, positions, H, dk, dv, gain)
+    if (dk <= 32) FG_LAUNCH(1);
+    else if (dk <= 64) FG_LAUNCH(2);
+    else if (dk <= 128) FG_LAUNCH(4);
+    else FG_LAUNCH(8);
+#undef FG_LAUNCH
+}
+
 MM_EXPORT int mm_forget_gate_walk(const void* q, const void* f, const void* v, int ldq, int ldf, int ldv, void* out, void* state,
                                   long long state_stride, const void* req_meta, const void* slots, const void* positions, int n_requests, int H,
                                   int dk, int dv, void* stream) {
@@ -742,17 +778,53 @@ MM_EXPORT int mm_forget_gate_walk(const void* q, const void* f, const void* v, i
     MM_REQUIRE(dk <= 256, "forget gate walk: key sizes above 256 are not supported");
     MM_REQUIRE(state != nullptr && slots != nullptr && positions != nullptr, "forget gate walk: the state and the positions are needed");
     if (n_requests <= 0) return MM_OK;
-    const dim3 grid(ceil_div(dv, FG_COLS), H, n_requests);
-    const size_t smem = sizeof(float) * FG_AHEAD * (2 * (size_t)dk + 2 * FG_COLS);
+    fg_walk_launch<0>(dim3(ceil_div(dv, FG_COLS), H, n_requests), (cudaStream_t)stream, (const float*)q, (const float*)f, (const float*)v, ldq, ldf, ldv,
+                      (float*)out, (float*)state, state_stride, (const int32_t*)req_meta, (const int32_t*)slots, (const int32_t*)positions, H, dk, dv,
+                      (float*)nullptr);
+    MM_CHECK_LAUNCH();
+    return MM_OK;
+}
+
+// The carry between the two chunk passes: a thread per number of the state.  scratch [chunks, H * dv * dk] holds what every
+// chunk adds and gets what every chunk starts from; gain [chunks, H * dk] the product of the chunk's gates per key channel.
+__global__ void forget_gate_carry_kernel(float* __restrict__ scratch, const float* __restrict__ gain, float* __restrict__ state, long long state_stride,
+                                         const int32_t* __restrict__ chunk_meta, const int32_t* __restrict__ req_chunks,
+                                         const int32_t* __restrict__ slots, const int32_t* __restrict__ positions, int H, int dk, int dv, long long size) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const int r = blockIdx.y;
+    if (i >= size) return;
+    const int first = req_chunks[2 * r], count = req_chunks[2 * r + 1];
+    if (count <= 0) return;
+    const int h = (int)(i / ((long long)dv * dk)), ch = (int)(i % dk);
+    float* st = state + (size_t)slots[r] * state_stride + i;
+    float S = positions[chunk_meta[4 * first]] == 0 ? 0.0f : *st;
+    for (int c = first; c < first + count; ++c) {
+        const float add = scratch[(size_t)c * size + i];
+        scratch[(size_t)c * size + i] = S;
+        S = fmaf(gain[((size_t)c * H + h) * dk + ch], S, add);
+    }
+    *st = S;
+}
+
+// Long portions chunk by chunk (three launches).  chunk_meta [chunks, 4] = (first token, tokens, request, .), req_chunks
+// [requests, 2] = (first chunk, chunks); scratch fp32 [chunks, H * dv * dk], gain fp32 [chunks, H * dk].
+MM_EXPORT int mm_forget_gate_chunked(const void* q, const void* f, const void* v, int ldq, int ldf, int ldv, void* out, void* state,
+                                     long long state_stride, const void* chunk_meta, const void* req_chunks, const void* slots, const void* positions,
+                                     int n_requests, int n_chunks, int H, int dk, int dv, void* scratch, void* gain, void* stream) {
+    MM_REQUIRE(H > 0 && dk > 0 && dv > 0 && dk <= 256, "forget gate walk: bad sizes, or a key size above 256");
+    MM_REQUIRE(state && slots && positions && chunk_meta && req_chunks && scratch && gain, "forget gate walk: the chunked walk needs its lists and its scratch");
+    if (n_requests <= 0 || n_chunks <= 0) return MM_OK;
     cudaStream_t s = (cudaStream_t)stream;
-#define FG_LAUNCH(PER)                                                                                                                          \
-    mm_launch(forget_gate_walk_kernel<PER>, grid, dim3(256), smem, s, (const float*)q, (const float*)f, (const float*)v, ldq, ldf, ldv, (float*)out, \
-              (float*)state, state_stride, (const int32_t*)req_meta, (const int32_t*)slots, (const int32_t*)positions, H, dk, dv)
-    if (dk <= 32) FG_LAUNCH(1);
-    else if (dk <= 64) FG_LAUNCH(2);
-    else if (dk <= 128) FG_LAUNCH(4);
-    else FG_LAUNCH(8);
-#undef FG_LAUNCH
+    const long long size = (long long)H * dv * dk;
+    const dim3 grid(ceil_div(dv, FG_COLS), H, n_chunks);
+    fg_walk_launch<1>(grid, s, (const float*)q, (const float*)f, (const float*)v, ldq, ldf, ldv, (float*)out, (float*)scratch, size,
+                      (const int32_t*)chunk_meta, (const int32_t*)slots, (const int32_t*)positions, H, dk, dv, (float*)gain);
+    MM_CHECK_LAUNCH();
+    mm_launch(forget_gate_carry_kernel, dim3(ceil_div(size, 256), n_requests), dim3(256), 0, s, (float*)scratch, (const float*)gain, (float*)state,
+              state_stride, (const int32_t*)chunk_meta, (const int32_t*)req_chunks, (const int32_t*)slots, (const int32_t*)positions, H, dk, dv, size);
+    MM_CHECK_LAUNCH();
+    fg_walk_launch<2>(grid, s, (const float*)q, (const float*)f, (const float*)v, ldq, ldf, ldv, (float*)out, (float*)scratch, size,
+                      (const int32_t*)chunk_meta, (const int32_t*)slots, (const int32_t*)positions, H, dk, dv, (float*)nullptr);
     MM_CHECK_LAUNCH();
     return MM_OK;
 }

@@ -318,7 +318,7 @@ def paged_talking_attention(q, cache, out, ctx, num_heads: int, num_kv_heads: in
         keys = min(window, ctx.max_kv_len) if window > 0 else ctx.max_kv_len
         splits = 1
         if n_tiles < TALKING_TARGET_CTAS // 2:
-            splits = max(1, min(-(-TALKING_TARGET_CTAS // n_tiles), -(-keys // 128), TALKING_MAX_SPLITS))
+            splits = max(1, min(-(-TALKING_TARGET_CTAS // n_tiles), -(-keys // 64), TALKING_MAX_SPLITS))
         part_o = part_ml = None
         if splits > 1:
             skey = ("talking_attention_scratch", n, num_heads, splits, value_dim)

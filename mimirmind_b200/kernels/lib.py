@@ -92,6 +92,7 @@ _PROTOTYPES = {
     "mm_attention_talking": [P, P, P, P, I, P, P, I, P, P, P, I, I, I, I, I, I, I, I, F, P, P, P],
     "mm_forget_gate_prep": [P, I, I, I, I, I, I, P, P, P],
     "mm_forget_gate_walk": [P, P, P, I, I, I, P, P, c_longlong, P, P, P, I, I, I, I, P],
+    "mm_forget_gate_chunked": [P, P, P, I, I, I, P, P, c_longlong, P, P, P, P, I, I, I, I, I, P, P, P],
     "mm_post_norm": [P, P, P, I, P, P, I, I, I, F, F, F, F, P],
     "mm_glu_rows": [P, I, c_longlong, P, I, I, I, I, F, P, P],
     "mm_cast_rows": [P, P, I, c_longlong, P],

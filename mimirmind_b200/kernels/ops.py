@@ -1523,6 +1523,34 @@ def forget_gate_walk(q: torch.Tensor, f: torch.Tensor, v: torch.Tensor, state: t
     return out
 
 
+def forget_gate_chunked(q: torch.Tensor, f: torch.Tensor, v: torch.Tensor, state: torch.Tensor, chunk_meta: torch.Tensor, req_chunks: torch.Tensor,
+                        slots: torch.Tensor, positions: torch.Tensor, heads: int, dk: int, dv: int) -> torch.Tensor:
+    """The same recurrence for long portions, chunk by chunk (three launches: every chunk from a zero state, the carry along
+    each request's chunks, every chunk again from its starting state).  ``chunk_meta`` [chunks, 4] = (first token, tokens,
+    request, .), ``req_chunks`` [requests, 2] = (first chunk, chunks)."""
+    for t, what in ((q, "q"), (f, "f"), (v, "v")):
+        if t.dtype != torch.float32 or not t.is_cuda or t.stride(1) != 1:
+            raise KernelError(f"forget gate walk {what}: fp32 rows with unit column stride are needed")
+    n = q.shape[0]
+    if q.shape[1] != heads * dk or f.shape != q.shape or v.shape != (n, heads * dv):
+        raise KernelError("forget gate walk: shape mismatch")
+    if state.dtype != torch.float32 or state.stride(-1) != 1 or state.shape[1] < heads * dv * dk:
+        raise KernelError("forget gate walk: the state is fp32 [slots, >= heads * dv * dk]")
+    _need(chunk_meta, "chunk_meta", torch.int32)
+    _need(req_chunks, "req_chunks", torch.int32)
+    _need(slots, "state slots", torch.int32)
+    _need(positions, "positions", torch.int32)
+    n_chunks, n_req = chunk_meta.shape[0], req_chunks.shape[0]
+    out = torch.empty((n, heads * dv), dtype=torch.float32, device=q.device)
+    scratch = torch.empty((max(1, n_chunks), heads * dv * dk), dtype=torch.float32, device=q.device)
+    gain = torch.empty((max(1, n_chunks), heads * dk), dtype=torch.float32, device=q.device)
+    check(_lib.load().mm_forget_gate_chunked(q.data_ptr(), f.data_ptr(), v.data_ptr(), q.stride(0), f.stride(0), v.stride(0), out.data_ptr(),
+                                             state.data_ptr(), state.stride(0), chunk_meta.data_ptr(), req_chunks.data_ptr(), slots.data_ptr(),
+                                             positions.data_ptr(), n_req, n_chunks, int(heads), int(dk), int(dv), scratch.data_ptr(), gain.data_ptr(),
+                                             _stream()), "forget_gate_chunked")
+    return out
+
+
 # ---- the norm after the sum, gated activations as a pass of their own (csrc/post_norm.cu) ------------------------------------------
 def post_norm(residual: torch.Tensor, a: Optional[torch.Tensor], b: Optional[torch.Tensor], weight: torch.Tensor, eps: float, alpha: float,
               ca: float = 1.0, cb: float = 1.0, out: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:

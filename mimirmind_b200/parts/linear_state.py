@@ -159,11 +159,14 @@ class LinearStateMixer(Mixer):
         a = linear(x, self.w_in, None, self.rt, out_dtype=torch.float32)
         state = cache.state
         if self.forget_gate:
-            # the walk is strictly token by token: one order of operations whatever the cutting, in either number format
             ops.forget_gate_prep(a, self.q_off, self.k_off, H * dk, self.f_bias, self.lower, silu_q=self.activation == "silu")
-            o = ops.forget_gate_walk(a[:, self.q_off:self.q_off + H * dk], a[:, self.k_off:self.k_off + H * dk],
-                                     a[:, self.v_off:self.v_off + H * dv], state, ctx.req_meta, ctx.state_slots, ctx.positions,
-                                     ctx.n_requests, H, dk, dv)
+            qs, fs, vs = a[:, self.q_off:self.q_off + H * dk], a[:, self.k_off:self.k_off + H * dk], a[:, self.v_off:self.v_off + H * dv]
+            # the 32-bit path keeps one order of operations whatever the cutting: it always walks token by token
+            if ctx.max_q_len >= CHUNKED_FROM and self.rt.dtype != torch.float32:
+                chunk_meta, req_chunks = token_chunks(ctx, CHUNK)
+                o = ops.forget_gate_chunked(qs, fs, vs, state, chunk_meta, req_chunks, ctx.state_slots, ctx.positions, H, dk, dv)
+            else:
+                o = ops.forget_gate_walk(qs, fs, vs, state, ctx.req_meta, ctx.state_slots, ctx.positions, ctx.n_requests, H, dk, dv)
             return self._finish(o, a)
         qkv, gate_rows = a, None          # where q, k and v stand, and (if elsewhere) the rows with the gates' columns
         if self.taps and ctx.max_q_len >= CONV_BY_TOKEN_FROM:

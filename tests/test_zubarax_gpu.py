@@ -238,6 +238,34 @@ def test_the_forget_gate_recurrence_against_the_plain_one(H, dk, dv):
         assert np.abs(g - want[r]).max() <= 2e-5 * max(1.0, np.abs(want[r]).max())
 
 
+@pytest.mark.parametrize("H,dk,dv", [(3, 16, 8), (2, 64, 40), (4, 128, 64), (1, 10, 7)])
+def test_chunks_walked_side_by_side_equal_the_walk(H, dk, dv):
+    """Long portions are cut into chunks of 64 tokens that are walked side by side; outputs and the states left in the
+    slots equal the walk's, for a request from position 0 in a slot somebody left full and one that goes on from a state."""
+    from mimirmind_b200.kernels import ops
+    rng = np.random.RandomState(dv)
+    lens, starts, slots = [300, 130, 64], [0, 77, 5], [1, 3, 0]
+    n = sum(lens)
+    q, v = dev(rng.randn(n, H * dk)), dev(rng.randn(n, H * dv))
+    f = dev(1.0 / (1.0 + np.exp(-2.0 * rng.randn(n, H * dk))))
+    state0 = rng.randn(4, H * dv * dk + 3)
+    q_start = np.concatenate([[0], np.cumsum(lens)[:-1]])
+    meta = i32([[int(q_start[r]), lens[r], starts[r] + lens[r], slots[r]] for r in range(3)])
+    positions = i32(sum([list(range(starts[r], starts[r] + lens[r])) for r in range(3)], []))
+    chunk_meta, req_chunks = [], []
+    for r in range(3):
+        first = len(chunk_meta)
+        for off in range(0, lens[r], 64):
+            chunk_meta.append([int(q_start[r]) + off, min(64, lens[r] - off), r, int(off == 0)])
+        req_chunks.append([first, len(chunk_meta) - first])
+    s_walk, s_chunk = dev(state0), dev(state0)
+    want = ops.forget_gate_walk(q, f, v, s_walk, meta, i32(slots), positions, 3, H, dk, dv).cpu().numpy()
+    got = ops.forget_gate_chunked(q, f, v, s_chunk, i32(chunk_meta), i32(req_chunks), i32(slots), positions, H, dk, dv).cpu().numpy()
+    assert np.abs(got - want).max() <= 2e-5 * max(1.0, np.abs(want).max())
+    assert np.abs(s_chunk.cpu().numpy() - s_walk.cpu().numpy()).max() <= 2e-5 * max(1.0, float(s_walk.abs().max()))
+    assert np.array_equal(s_chunk.cpu().numpy()[2], state0.astype(np.float32)[2])          # a slot nobody holds is not touched
+
+
 # ---- experts ----------------------------------------------------------------------------------------------------------------
 @pytest.mark.parametrize("E,top", [(6, 2), (5, 5), (8, 1), (64, 6), (3, 1)])
 def test_the_sigmoid_routers_choice(E, top):
