@@ -647,87 +647,89 @@ MM_EXPORT int mm_forget_gate_prep(void* x, int ld, int n_tokens, int q_off, int 
     return MM_OK;
 }
 
-// The walk: q, f fp32 rows with H heads of dk (row strides ldq, ldf), v with H heads of dv.  A block of 8 warps owns 8
-// columns of one head's S for one request, a warp one of them (the walk is a chain from token to token: what shortens it is
-// less work per warp and token, and the narrow blocks are many), a lane the entries lane, lane + 32, ... of its column;
-// q, f and v of FG_AHEAD tokens at a time are staged in shared memory.  The state's layout in a slot is [H, dv, dk], as in the walk
-// above; a request at position 0 starts from zero whatever its slot holds.
+// The walk: q, f fp32 rows with H heads of dk (row strides ldq, ldf), v with H heads of dv.  A block of 8 warps owns 32
+// columns of one head's S for one request (or chunk); eight lanes share a column, lane `ks` of them the entries
+// i = 32 (e / 4) + 4 ks + e % 4, e < PER, so that q and f of a token are read as 16-byte words without bank conflicts and
+// a token's read-out is a sum over eight lanes.  q, f and v of FG_AHEAD tokens at a time are staged in shared memory (rows
+// padded to 8 PER numbers; q is zero beyond dk, so the padding adds nothing).  The state's layout in a slot is [H, dv, dk],
+// as in the walk above; a request at position 0 starts from zero whatever its slot holds.
 #define FG_AHEAD 16
-#define FG_CW 1          // columns per warp
-#define FG_COLS (8 * FG_CW)
+#define FG_COLS 32
 // MODE 0: a request's tokens from its slot's state, which is left updated.  Long portions are cut into chunks that are walked
 // side by side, because the update is linear in S with a diagonal transition (S_end = diag(product of the f) S_start + what
-// the chunk adds): MODE 1 walks chunk blockIdx.z from zero and leaves what it adds in scratch and the product of its gates per
-// key channel in `gain` [chunks, H * dk]; a carry kernel walks each request's chunks in order, leaves every chunk's starting
-// state in scratch and the last state in the slot; MODE 2 walks every chunk again from its starting state and writes the
-// outputs.
+// the chunk adds): MODE 1 walks chunk blockIdx.z from zero and leaves what it adds in scratch (the products of the gates per
+// key channel are made by a kernel of their own); a carry kernel walks each request's chunks in order, leaves every chunk's
+// starting state in scratch and the last state in the slot; MODE 2 walks every chunk again from its starting state and
+// writes the outputs.
 template <int PER, int MODE>
 __global__ void __launch_bounds__(256) forget_gate_walk_kernel(const float* __restrict__ q, const float* __restrict__ f, const float* __restrict__ v,
                                                                int ldq, int ldf, int ldv, float* __restrict__ out, float* __restrict__ state,
                                                                long long state_stride, const int32_t* __restrict__ req_meta,
                                                                const int32_t* __restrict__ slots, const int32_t* __restrict__ positions, int H,
-                                                               int dk, int dv, float* __restrict__ gain) {
-    extern __shared__ float fg_smem[];
-    float* sq = fg_smem;                          // [AHEAD][dk]
-    float* sf = sq + FG_AHEAD * dk;               // [AHEAD][dk]
-    float* sv = sf + FG_AHEAD * dk;               // [AHEAD][COLS]
+                                                               int dk, int dv) {
+    constexpr int DKP = 8 * PER;
+    extern __shared__ __align__(16) float fg_smem[];
+    float* sq = fg_smem;                          // [AHEAD][DKP]
+    float* sf = sq + FG_AHEAD * DKP;              // [AHEAD][DKP]
+    float* sv = sf + FG_AHEAD * DKP;              // [AHEAD][COLS]
     float* so = sv + FG_AHEAD * FG_COLS;          // [AHEAD][COLS]
     const int h = blockIdx.y, r = blockIdx.z, col0 = blockIdx.x * FG_COLS;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int ks = lane & 7, cl = warp * 4 + (lane >> 3);
+    const int col = col0 + cl;
+    const bool col_ok = col < dv;
     const int t0 = req_meta ? req_meta[4 * r] : r;
     const int n = req_meta ? req_meta[4 * r + 1] : 1;
     const bool fresh = MODE == 1 || (MODE == 0 && positions[t0] == 0);
     // MODE 1, 2: r is a chunk, req_meta the chunk list, state the scratch with one set of matrices per chunk
-    float* st = state + (size_t)(MODE == 0 ? slots[r] : r) * state_stride + (size_t)h * dv * dk;
-    float prod[PER];
+    float* st = state + (size_t)(MODE == 0 ? slots[r] : r) * state_stride + ((size_t)h * dv + (col_ok ? col : 0)) * dk;
+    float S[PER];
 #pragma unroll
-    for (int e = 0; e < PER; ++e) prod[e] = 1.0f;
-    float S[FG_CW][PER];
-#pragma unroll
-    for (int c = 0; c < FG_CW; ++c) {
-        const int col = col0 + warp * FG_CW + c;
-#pragma unroll
-        for (int e = 0; e < PER; ++e) {
-            const int i = lane + 32 * e;
-            S[c][e] = (!fresh && col < dv && i < dk) ? st[(size_t)col * dk + i] : 0.0f;
-        }
+    for (int e = 0; e < PER; ++e) {
+        const int i = (e >> 2) * 32 + ks * 4 + (e & 3);
+        S[e] = (!fresh && col_ok && i < dk) ? st[i] : 0.0f;
     }
+    for (int i = threadIdx.x; i < 2 * FG_AHEAD * DKP; i += 256) fg_smem[i] = 0.0f;      // what no copy writes stays zero
     for (int base = 0; base < n; base += FG_AHEAD) {
         const int cnt = min(FG_AHEAD, n - base);
         __syncthreads();
         for (int idx = threadIdx.x; idx < cnt * dk; idx += 256) {
             const int tt = idx / dk, i = idx - tt * dk;
             const size_t t = (size_t)(t0 + base + tt);
-            sq[idx] = q[t * ldq + h * dk + i];
-            sf[idx] = f[t * ldf + h * dk + i];
+            sq[tt * DKP + i] = q[t * ldq + h * dk + i];
+            sf[tt * DKP + i] = f[t * ldf + h * dk + i];
         }
         for (int idx = threadIdx.x; idx < cnt * FG_COLS; idx += 256) {
             const int tt = idx / FG_COLS, c = idx - tt * FG_COLS;
             sv[idx] = col0 + c < dv ? v[(size_t)(t0 + base + tt) * ldv + h * dv + col0 + c] : 0.0f;
         }
         __syncthreads();
+#pragma unroll 4
         for (int tt = 0; tt < cnt; ++tt) {
-            float qq[PER], ff[PER];
+            const float4* q4 = reinterpret_cast<const float4*>(sq + tt * DKP) + ks;
+            const float4* f4 = reinterpret_cast<const float4*>(sf + tt * DKP) + ks;
+            const float vv = sv[tt * FG_COLS + cl];
+            float d0 = 0.0f, d1 = 0.0f, d2 = 0.0f, d3 = 0.0f;
 #pragma unroll
-            for (int e = 0; e < PER; ++e) {
-                const int i = lane + 32 * e;
-                qq[e] = i < dk ? sq[tt * dk + i] : 0.0f;
-                ff[e] = i < dk ? sf[tt * dk + i] : 1.0f;
-                if (MODE == 1) prod[e] *= ff[e];
-            }
-#pragma unroll
-            for (int c = 0; c < FG_CW; ++c) {
-                const float vv = sv[tt * FG_COLS + warp * FG_CW + c];
-                float dot = 0.0f;
-#pragma unroll
-                for (int e = 0; e < PER; ++e) {
-                    S[c][e] = fmaf(ff[e], S[c][e], (1.0f - ff[e]) * vv);
-                    if (MODE != 1) dot = fmaf(S[c][e], qq[e], dot);
-                }
+            for (int j = 0; j < PER / 4; ++j) {
+                const float4 fv = f4[j * 8];
+                S[4 * j] = fmaf(fv.x, S[4 * j], (1.0f - fv.x) * vv);
+                S[4 * j + 1] = fmaf(fv.y, S[4 * j + 1], (1.0f - fv.y) * vv);
+                S[4 * j + 2] = fmaf(fv.z, S[4 * j + 2], (1.0f - fv.z) * vv);
+                S[4 * j + 3] = fmaf(fv.w, S[4 * j + 3], (1.0f - fv.w) * vv);
                 if (MODE != 1) {
-                    dot = warp_sum(dot);
-                    if (lane == 0) so[tt * FG_COLS + warp * FG_CW + c] = dot;
+                    const float4 qv = q4[j * 8];
+                    d0 = fmaf(S[4 * j], qv.x, d0);
+                    d1 = fmaf(S[4 * j + 1], qv.y, d1);
+                    d2 = fmaf(S[4 * j + 2], qv.z, d2);
+                    d3 = fmaf(S[4 * j + 3], qv.w, d3);
                 }
+            }
+            if (MODE != 1) {
+                float dot = (d0 + d1) + (d2 + d3);
+#pragma unroll
+                for (int o = 1; o < 8; o <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+                if (ks == 0) so[tt * FG_COLS + cl] = dot;
             }
         }
         __syncthreads();
@@ -737,37 +739,38 @@ __global__ void __launch_bounds__(256) forget_gate_walk_kernel(const float* __re
                 if (col0 + c < dv) out[(size_t)(t0 + base + tt) * H * dv + h * dv + col0 + c] = so[idx];
             }
     }
-    if (MODE == 1 && blockIdx.x == 0 && warp == 0) {
+    if (MODE == 2 || !col_ok) return;
 #pragma unroll
-        for (int e = 0; e < PER; ++e) {
-            const int i = lane + 32 * e;
-            if (i < dk) gain[((size_t)r * H + h) * dk + i] = prod[e];
-        }
+    for (int e = 0; e < PER; ++e) {
+        const int i = (e >> 2) * 32 + ks * 4 + (e & 3);
+        if (i < dk) st[i] = S[e];
     }
-    if (MODE == 2) return;
-#pragma unroll
-    for (int c = 0; c < FG_CW; ++c) {
-        const int col = col0 + warp * FG_CW + c;
-        if (col >= dv) continue;
-#pragma unroll
-        for (int e = 0; e < PER; ++e) {
-            const int i = lane + 32 * e;
-            if (i < dk) st[(size_t)col * dk + i] = S[c][e];
-        }
-    }
+}
+
+// The product of a chunk's gates per head and key channel: gain [chunks, H * dk]; f fp32 rows with row stride ldf.
+__global__ void forget_gate_gain_kernel(const float* __restrict__ f, int ldf, const int32_t* __restrict__ chunk_meta, float* __restrict__ gain, int width) {
+    const int c = blockIdx.y;
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= width) return;
+    const int t0 = chunk_meta[4 * c], n = chunk_meta[4 * c + 1];
+    float p = 1.0f;
+    for (int t = 0; t < n; ++t) p *= f[(size_t)(t0 + t) * ldf + i];
+    gain[(size_t)c * width + i] = p;
 }
 
 template <int MODE>
 static void fg_walk_launch(dim3 grid, cudaStream_t s, const float* q, const float* f, const float* v, int ldq, int ldf, int ldv, float* out, float* state,
-                           long long state_stride, const int32_t* req_meta, const int32_t* slots, const int32_t* positions, int H, int dk, int dv,
-                           float* gain) {
-    const size_t smem = sizeof(float) * FG_AHEAD * (2 * (size_t)dk + 2 * FG_COLS);
-#define FG_LAUNCH(PER) \
-    mm_launch(forget_gate_walk_kernel<PER, MODE>, grid, dim3(256), smem, s, q, f, v, ldq, ldf, ldv, out, state, state_stride, req_meta, slots, positions, H, dk, dv, gain)
-    if (dk <= 32) FG_LAUNCH(1);
-    else if (dk <= 64) FG_LAUNCH(2);
-    else if (dk <= 128) FG_LAUNCH(4);
-    else FG_LAUNCH(8);
+                           long long state_stride, const int32_t* req_meta, const int32_t* slots, const int32_t* positions, int H, int dk, int dv) {
+#define FG_LAUNCH(PER)                                                                                                                         \
+    do {                                                                                                                                       \
+        const size_t smem = sizeof(float) * FG_AHEAD * (2 * 8 * PER + 2 * FG_COLS);                                                             \
+        mm_launch(forget_gate_walk_kernel<PER, MODE>, grid, dim3(256), smem, s, q, f, v, ldq, ldf, ldv, out, state, state_stride, req_meta, slots, \
+                  positions, H, dk, dv);                                                                                                       \
+    } while (0)
+    if (dk <= 32) FG_LAUNCH(4);
+    else if (dk <= 64) FG_LAUNCH(8);
+    else if (dk <= 128) FG_LAUNCH(16);
+    else FG_LAUNCH(32);
 #undef FG_LAUNCH
 }
 
@@ -779,8 +782,7 @@ MM_EXPORT int mm_forget_gate_walk(const void* q, const void* f, const void* v, i
     MM_REQUIRE(state != nullptr && slots != nullptr && positions != nullptr, "forget gate walk: the state and the positions are needed");
     if (n_requests <= 0) return MM_OK;
     fg_walk_launch<0>(dim3(ceil_div(dv, FG_COLS), H, n_requests), (cudaStream_t)stream, (const float*)q, (const float*)f, (const float*)v, ldq, ldf, ldv,
-                      (float*)out, (float*)state, state_stride, (const int32_t*)req_meta, (const int32_t*)slots, (const int32_t*)positions, H, dk, dv,
-                      (float*)nullptr);
+                      (float*)out, (float*)state, state_stride, (const int32_t*)req_meta, (const int32_t*)slots, (const int32_t*)positions, H, dk, dv);
     MM_CHECK_LAUNCH();
     return MM_OK;
 }
@@ -818,13 +820,16 @@ MM_EXPORT int mm_forget_gate_chunked(const void* q, const void* f, const void* v
     const long long size = (long long)H * dv * dk;
     const dim3 grid(ceil_div(dv, FG_COLS), H, n_chunks);
     fg_walk_launch<1>(grid, s, (const float*)q, (const float*)f, (const float*)v, ldq, ldf, ldv, (float*)out, (float*)scratch, size,
-                      (const int32_t*)chunk_meta, (const int32_t*)slots, (const int32_t*)positions, H, dk, dv, (float*)gain);
+                      (const int32_t*)chunk_meta, (const int32_t*)slots, (const int32_t*)positions, H, dk, dv);
+    MM_CHECK_LAUNCH();
+    mm_launch(forget_gate_gain_kernel, dim3(ceil_div((long long)H * dk, 128), n_chunks), dim3(128), 0, s, (const float*)f, ldf, (const int32_t*)chunk_meta,
+              (float*)gain, H * dk);
     MM_CHECK_LAUNCH();
     mm_launch(forget_gate_carry_kernel, dim3(ceil_div(size, 256), n_requests), dim3(256), 0, s, (float*)scratch, (const float*)gain, (float*)state,
               state_stride, (const int32_t*)chunk_meta, (const int32_t*)req_chunks, (const int32_t*)slots, (const int32_t*)positions, H, dk, dv, size);
     MM_CHECK_LAUNCH();
     fg_walk_launch<2>(grid, s, (const float*)q, (const float*)f, (const float*)v, ldq, ldf, ldv, (float*)out, (float*)scratch, size,
-                      (const int32_t*)chunk_meta, (const int32_t*)slots, (const int32_t*)positions, H, dk, dv, (float*)nullptr);
+                      (const int32_t*)chunk_meta, (const int32_t*)slots, (const int32_t*)positions, H, dk, dv);
     MM_CHECK_LAUNCH();
     return MM_OK;
 }
