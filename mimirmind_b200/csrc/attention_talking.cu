@@ -370,37 +370,43 @@ __global__ void __launch_bounds__(512) attention_talking_mma_kernel(
     }
     const int ksteps = dk / 16;
     const int id = lane >> 3, rr = lane & 7;
+    const int kparts = dk / 8, vparts = DV / 8;
+    const int most = kparts > vparts ? kparts : vparts;
+    const int row_shift = most <= 4 ? 2 : (most <= 8 ? 3 : (most <= 16 ? 4 : 5));      // dk <= 256: at most 32 copies a row
+    const int row_threads = 1 << row_shift;
+    const int page_shift = (page_size & (page_size - 1)) == 0 ? __ffs(page_size) - 1 : -1;
 
     for (int kt = kt0; kt < kt1; ++kt) {
         const int key0 = kt * TK;
         __syncthreads();                        // the tile before is used up (and, the first time, Q and T are written)
-        const int kparts = dk / 8, vparts = DV / 8;
-        for (int i = tid; i < G * TK * kparts; i += threads) {
-            const int part = i % kparts, key = (i / kparts) % TK, g = i / (kparts * TK);
+        // a row of the tile (kv head, key) is copied by `row_threads` neighbouring threads, 16 bytes each: no division per copy
+        for (int row = tid >> row_shift; row < G * TK; row += threads >> row_shift) {
+            const int g = row / TK, key = row % TK;          // TK is a power of two
             const int j = key0 + key;
-            __nv_bfloat16* dst = sK + ((size_t)g * TK + key) * KS + part * 8;
-            if (j >= lo_all && j < hi_all) {
-                const size_t page = (size_t)table[j / page_size];
-                cp_async16(dst, k_pages + ((page * G + g) * page_size + (size_t)(j % page_size)) * dk + part * 8);
-            } else {
-                *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+            const int part = tid & (row_threads - 1);
+            const bool seen = j >= lo_all && j < hi_all;
+            size_t at = 0;
+            if (seen) {
+                const int pg = page_shift >= 0 ? j >> page_shift : j / page_size;
+                at = ((size_t)table[pg] * G + g) * page_size + (size_t)(j - pg * page_size);
             }
-        }
-        for (int i = tid; i < G * TK * vparts; i += threads) {
-            const int part = i % vparts, key = (i / vparts) % TK, g = i / (vparts * TK);
-            const int j = key0 + key;
-            __nv_bfloat16* dst = sV + ((size_t)g * TK + key) * VS + part * 8;
-            if (j >= lo_all && j < hi_all) {
-                const size_t page = (size_t)table[j / page_size];
-                cp_async16(dst, v_pages + ((page * G + g) * page_size + (size_t)(j % page_size)) * DV + part * 8);
-            } else {
-                *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+            if (part < kparts) {
+                __nv_bfloat16* dst = sK + ((size_t)g * TK + key) * KS + part * 8;
+                if (seen) cp_async16(dst, k_pages + at * dk + part * 8);
+                else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+            }
+            if (part < vparts) {
+                __nv_bfloat16* dst = sV + ((size_t)g * TK + key) * VS + part * 8;
+                if (seen) cp_async16(dst, v_pages + at * DV + part * 8);
+                else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
             }
         }
         cp_async_commit();
         cp_async_wait<0>();
         __syncthreads();
 
+        // a tile whose keys all lie at or before the first row's position and inside the last row's window needs no masks
+        const bool interior = key0 + TK - 1 <= pos0 && (window == 0 || key0 >= pos0 + 15 + 1 - window);
         // raw scores of the heads this warp takes in this phase
         float s[2][NT_S][4];
 #pragma unroll
@@ -476,18 +482,30 @@ __global__ void __launch_bounds__(512) attention_talking_mma_kernel(
             if (hl >= Hc || h >= H) continue;
             float (&mx)[NT_S][4] = mxs[x];
             float new_lo = m_lo[x], new_hi = m_hi[x];
+            if (interior) {
+                // every key of the tile is seen by every row: no masks (rows beyond the tile's tokens hold zeros and are never stored)
 #pragma unroll
-            for (int j = 0; j < NT_S; ++j)
+                for (int j = 0; j < NT_S; ++j)
 #pragma unroll
-                for (int c = 0; c < 2; ++c) {
-                    const int key = key0 + j * 8 + (lane & 3) * 2 + c;
-                    const bool ok_lo = valid_lo && key <= pos_lo && key >= wlo_lo;
-                    const bool ok_hi = valid_hi && key <= pos_hi && key >= wlo_hi;
-                    mx[j][c] = ok_lo ? mx[j][c] * TALK_LOG2E : -INFINITY;
-                    mx[j][2 + c] = ok_hi ? mx[j][2 + c] * TALK_LOG2E : -INFINITY;
-                    new_lo = fmaxf(new_lo, mx[j][c]);
-                    new_hi = fmaxf(new_hi, mx[j][2 + c]);
-                }
+                    for (int c = 0; c < 4; ++c) {
+                        mx[j][c] *= TALK_LOG2E;
+                        if (c < 2) new_lo = fmaxf(new_lo, mx[j][c]);
+                        else new_hi = fmaxf(new_hi, mx[j][c]);
+                    }
+            } else {
+#pragma unroll
+                for (int j = 0; j < NT_S; ++j)
+#pragma unroll
+                    for (int c = 0; c < 2; ++c) {
+                        const int key = key0 + j * 8 + (lane & 3) * 2 + c;
+                        const bool ok_lo = valid_lo && key <= pos_lo && key >= wlo_lo;
+                        const bool ok_hi = valid_hi && key <= pos_hi && key >= wlo_hi;
+                        mx[j][c] = ok_lo ? mx[j][c] * TALK_LOG2E : -INFINITY;
+                        mx[j][2 + c] = ok_hi ? mx[j][2 + c] * TALK_LOG2E : -INFINITY;
+                        new_lo = fmaxf(new_lo, mx[j][c]);
+                        new_hi = fmaxf(new_hi, mx[j][2 + c]);
+                    }
+            }
             new_lo = fmaxf(new_lo, __shfl_xor_sync(0xffffffffu, new_lo, 1));
             new_lo = fmaxf(new_lo, __shfl_xor_sync(0xffffffffu, new_lo, 2));
             new_hi = fmaxf(new_hi, __shfl_xor_sync(0xffffffffu, new_hi, 1));
