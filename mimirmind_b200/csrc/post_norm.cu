@@ -32,6 +32,74 @@ __global__ void __launch_bounds__(256) post_norm_kernel(float* __restrict__ x, c
     }
 }
 
+// Eight numbers at a time (16-byte words of bfloat16, two of fp32): the same arithmetic in the same order per element.
+__device__ __forceinline__ void pn_load8(const float* p, float* v) {
+    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+__device__ __forceinline__ void pn_load8(const __nv_bfloat16* p, float* v) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 f = __bfloat1622float2(h[i]);
+        v[2 * i] = f.x;
+        v[2 * i + 1] = f.y;
+    }
+}
+__device__ __forceinline__ void pn_store8(float* p, const float* v) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
+}
+__device__ __forceinline__ void pn_store8(__nv_bfloat16* p, const float* v) {
+    uint4 raw;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+    *reinterpret_cast<uint4*>(p) = raw;
+}
+
+template <typename TB, typename TO>
+__global__ void __launch_bounds__(256) post_norm8_kernel(float* __restrict__ x, const TB* __restrict__ a, const TB* __restrict__ b,
+                                                         const float* __restrict__ w, TO* __restrict__ out, int D, float alpha, float ca, float cb,
+                                                         float eps) {
+    extern __shared__ __align__(16) float pn_row[];
+    __shared__ float scratch[32];
+    const size_t t = blockIdx.x;
+    float* xr = x + t * D;
+    float ss = 0.0f;
+    for (int i = threadIdx.x * 8; i < D; i += blockDim.x * 8) {
+        float y[8], u[8];
+        pn_load8(xr + i, y);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) y[e] *= alpha;
+        if (a) {
+            pn_load8(a + t * D + i, u);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) y[e] = fmaf(ca, u[e], y[e]);
+        }
+        if (b) {
+            pn_load8(b + t * D + i, u);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) y[e] = fmaf(cb, u[e], y[e]);
+        }
+#pragma unroll
+        for (int e = 0; e < 8; ++e) ss = fmaf(y[e], y[e], ss);
+        pn_store8(pn_row + i, y);
+    }
+    ss = block_sum(ss, scratch);
+    const float r = 1.0f / sqrtf(ss / (float)D + eps);
+    for (int i = threadIdx.x * 8; i < D; i += blockDim.x * 8) {
+        float y[8], wv[8];
+        pn_load8(pn_row + i, y);
+        pn_load8(w + i, wv);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) y[e] = y[e] * r * wv[e];
+        pn_store8(xr + i, y);
+        if (out) pn_store8(out + t * D + i, y);
+    }
+}
+
 // x [n, D] fp32 residual (in place); a, b [n, D] of dtype `b_dtype` or null; w fp32 [D]; out [n, D] of `out_dtype` or null.
 MM_EXPORT int mm_post_norm(void* x, const void* a, const void* b, int b_dtype, const void* w, void* out, int out_dtype, int n, int D, float alpha,
                            float ca, float cb, float eps, void* stream) {
@@ -41,9 +109,10 @@ MM_EXPORT int mm_post_norm(void* x, const void* a, const void* b, int b_dtype, c
     cudaStream_t s = (cudaStream_t)stream;
     const size_t smem = (size_t)D * sizeof(float);
     typedef __nv_bfloat16 bf;
+    const bool by8 = D % 8 == 0 && (((uintptr_t)x | (uintptr_t)a | (uintptr_t)b | (uintptr_t)w | (uintptr_t)out) & 15) == 0;
 #define PN_LAUNCH(TB, TO)                                                                                                         \
     do {                                                                                                                          \
-        auto kernel = post_norm_kernel<TB, TO>;                                                                                   \
+        auto kernel = by8 ? post_norm8_kernel<TB, TO> : post_norm_kernel<TB, TO>;                                                 \
         if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);               \
         mm_launch(kernel, dim3(n), dim3(256), smem, s, (float*)x, (const TB*)a, (const TB*)b, (const float*)w, (TO*)out, D, alpha, ca, cb, eps); \
     } while (0)
