@@ -417,6 +417,7 @@ __global__ void __launch_bounds__(512) attention_talking_mma_kernel(
             if (g < H) {
                 const __nv_bfloat16* tQ = sQ + (size_t)g * 16 * KS;
                 const __nv_bfloat16* tK = sK + (size_t)(g / rep) * TK * KS;
+#pragma unroll 2
                 for (int ks = 0; ks < ksteps; ++ks) {
                     uint32_t qf[4];
                     ldmatrix_x4(qf[0], qf[1], qf[2], qf[3], tQ + ((id & 1) * 8 + rr) * KS + ks * 16 + (id >> 1) * 8);
@@ -454,6 +455,7 @@ __global__ void __launch_bounds__(512) attention_talking_mma_kernel(
             for (int j = 0; j < NT_S; ++j) mxs[x][j][0] = mxs[x][j][1] = mxs[x][j][2] = mxs[x][j][3] = 0.0f;
         if (warp * HPW < Hc) {
             const float* th = sT + (size_t)warp * HPW * H;
+#pragma unroll 4
             for (int g = 0; g < H; ++g) {
                 float t[HPW];
 #pragma unroll

@@ -800,10 +800,22 @@ __global__ void forget_gate_carry_kernel(float* __restrict__ scratch, const floa
     const int h = (int)(i / ((long long)dv * dk)), ch = (int)(i % dk);
     float* st = state + (size_t)slots[r] * state_stride + i;
     float S = positions[chunk_meta[4 * first]] == 0 ? 0.0f : *st;
-    for (int c = first; c < first + count; ++c) {
-        const float add = scratch[(size_t)c * size + i];
-        scratch[(size_t)c * size + i] = S;
-        S = fmaf(gain[((size_t)c * H + h) * dk + ch], S, add);
+    // eight chunks at a time: their loads are issued together, then the chain of eight multiply-adds runs
+    for (int c0 = first; c0 < first + count; c0 += 8) {
+        float add[8], gn[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const bool in = c0 + j < first + count;
+            add[j] = in ? scratch[(size_t)(c0 + j) * size + i] : 0.0f;
+            gn[j] = in ? gain[((size_t)(c0 + j) * H + h) * dk + ch] : 1.0f;
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            if (c0 + j < first + count) {
+                scratch[(size_t)(c0 + j) * size + i] = S;
+                S = fmaf(gn[j], S, add[j]);
+            }
+        }
     }
     *st = S;
 }
