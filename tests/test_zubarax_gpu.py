@@ -415,7 +415,7 @@ def test_every_layer_run_against_the_plain_stream(models):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name,page_size", [("A", 16), ("B", 16), ("C", 8), ("A", 32)])
+@pytest.mark.parametrize("name,page_size", [("A", 16), ("B", 16), ("C", 8), ("A", 32), ("D", 16)])
 def test_every_way_of_cutting_matches_the_plain_implementation(name, page_size, dtype, models):
     folder, cfg, w = models(name, dtype)
     reqs = {f"{name}{i}": random_tokens(cfg["vocab"], n, 100 * i + n) for i, n in enumerate(zu.LENGTHS[name])}

@@ -74,8 +74,16 @@ CONFIGS = {
         parallel((5, 5, 9, 7, 0.33, 2, (4, 50.0)), (3, 10, 5), (0.9, 0.9), moe(33, 0.7, 5, 5, (17, 3.0))),
         parallel((6, 2, 10, 12, 0.3, 1, None), (1, 12, 6), (1.0, 2.0), moe(17, 1.0, 3, 1)),
     ], [0, 0, 1])),
+    # a wider model whose attention sizes the tensor-core kernel takes in its other forms: twelve heads of wide values (a head
+    # per warp), a key size that is an odd multiple of 16, three heads over one key head, part of a head rotated, values wider
+    # than keys
+    "D": config(1000, 384, 1e-5, 2.5, 12.0, _with_repeats([
+        parallel((12, 4, 80, 96, 0.11, 4, (40, 500000.0)), (3, 48, 80), (0.8, 1.1), moe(160, 1.0, 6, 2, (96, 1.0))),
+        parallel((3, 1, 144, 32, 0.08, 3, (144, 10000.0)), (2, 64, 64), (1.0, 0.7), moe(64, 2.0, 4, 1)),
+        parallel((8, 8, 32, 128, 0.18, 2, (16, 1000.0)), (4, 32, 32), (1.2, 1.0), moe(96, 1.5, 5, 3, (64, 0.5))),
+    ], [0, 1, 2, 0, 1, 2])),
 }
-LENGTHS = {"A": [1, 9, 77, 300], "B": [5, 70, 280], "C": [2, 33, 150, 270]}
+LENGTHS = {"A": [1, 9, 77, 300], "B": [5, 70, 280], "C": [2, 33, 150, 270], "D": [3, 120, 333]}
 
 
 def every_expert_chosen(cfg):
