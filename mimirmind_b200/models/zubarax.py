@@ -12,7 +12,7 @@ norms are RMS norms whose weight is stored around zero (``1 + w`` multiplies).  
   strength of the write; silu on q, an RMS norm per head with one weight for all heads.
 
 Feed-forward: routed experts with sigmoid scores that are not renormed and multiply the expert's *input*, experts of the
-clamped form ``g sigmoid(1.702 g) (u + 1)``, and a shared expert of the same form for every token.  A layer may run with
+clamped form ``g sigmoid(1.702 g) (u + 1)``, and one more such expert that no router gates.  A layer may run with
 another layer's tensors (``weights_of``): it is then a schedule entry of that layer, with a cache and state of its own.
 The embedding is scaled; the head is the embedding table itself.
 Tensor names: ``embed``, ``l<i>.norm1|norm2``, ``l<i>.mix.left.*``, ``l<i>.mix.right.*``, ``l<i>.mlp.*``, ``final.norm``.

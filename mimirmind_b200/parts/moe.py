@@ -9,7 +9,7 @@ Further options, each a parameter.  ``scoring`` ``sigmoid``: ``s = sigmoid(z)`` 
 ``s`` as it is.  ``weight_on`` ``input``: the weight multiplies the expert's input, the output is ``sum_e expert_e(w_e h)``
 (both of an expert's first products are linear, so the weight is applied to their results in fp32).  ``activation``
 ``clamped`` with ``limit``: ``g = min(W_gate h, limit)``, ``u = clamp(W_up h, -limit, limit)``, ``y = g sigmoid(1.702 g) (u + 1)``.
-``shared``: the PartSpec of a feed-forward that runs for every token and is added.
+``shared``: the PartSpec of a feed-forward that every token goes through beside its routed experts; the two results add up.
 
 The experts' matrices are stacked at load (``[E, 2F, D]`` gate and up rows, ``[E, D, F]``).  A step routes on the
 device, puts the rows of every expert side by side, and runs two grouped products over them: for prompt-sized steps in

@@ -11,7 +11,8 @@ keys of size ``key_dim`` and values of size ``value_dim``.  Options, each a para
   with ``i + dims/2``, angle ``p base^(-2i/dims)``;
 * ``v_unit``: every value head is divided by its root mean square (no weight) and cached so;
 * ``talk``: a matrix ``[H, H]``; the scaled scores of one (query, key) pair are mixed, ``s_h = sum_g talk[h, g] r_g``;
-* ``sink``: one learned logit per head whose ``exp`` joins the softmax's denominator (no key, no value, not scaled);
+* ``sink``: one learned logit per head whose ``exp`` joins the softmax's denominator: it stands for no token, so nothing
+  is added to the output for it, and the score scale does not touch it;
 * ``window``: 0 (causal over everything) or the number of keys a query sees, itself included.
 
 One product makes q, k and v as fp32 rows; convolution, norms and rotation read those (``csrc/linear_state.cu``,

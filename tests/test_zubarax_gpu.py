@@ -149,7 +149,7 @@ def test_the_learned_sink_takes_its_share(dtype, route):
     if dtype == "bfloat16":
         q, k, v = bf16_round(q), bf16_round(k), bf16_round(v)
     kp, vp, table = _paged(k, v, page, rng, DT[dtype])
-    sink = np.array([40.0, -40.0, 0.0])      # drowns head 0, vanishes from head 1, counts once in head 2
+    sink = np.array([40.0, -40.0, 0.0])      # drowns head 0, vanishes from head 1, weighs as much as one key of score 0 in head 2
     for single in (False, True):
         got = _attend(q, kp, vp, table, page, 60, T, H, G, dk, dv, 0.2, dtype, None, sink, single=single)
         want = pz.talking_sink_attention_core(q, k, v, np.eye(H), sink, 0.2)[60:]
